@@ -10,8 +10,8 @@ in a page.  For every kind of need, a `CacheKind` says
   * for slots: the tensor [slots, ...] of one layer and how a slot is cleared.
 A kind is registered for the class of its spec (`register_cache_kind`), from
 anywhere: a test registers a cache of one latent vector per position without
-touching this package.  Keys and values in pages (`PagedKV`) and fixed-size state
-(`FixedState`) are registered here.
+touching this package.  Keys and values in pages (`PagedKV`), one latent row per
+position in pages (`PagedLatent`) and fixed-size state (`FixedState`) are registered here.
 """
 from __future__ import annotations
 
@@ -20,7 +20,7 @@ from typing import Dict, Optional
 
 import torch
 
-from ..parts.base import CacheParts, FixedState, PagedKV  # noqa: F401  (CacheParts: part of this module's interface)
+from ..parts.base import CacheParts, FixedState, PagedKV, PagedLatent  # noqa: F401  (CacheParts: part of this module's interface)
 
 
 @dataclass
@@ -113,6 +113,23 @@ class PagedKVKind(CacheKind):
         return LayerCache(group, True, k, v, None, flat)
 
 
+class PagedLatentKind(CacheKind):
+    """One row per position: [layer, page, 1, offset in page, width].  The mixer is handed the same tensor as
+    `k_pool` and `v_pool` (and `pages`): an attention kernel reads it as one key/value head whose value is
+    the first part of the key's row."""
+
+    def page_bytes(self, spec: PagedLatent, page_size, element_bytes):
+        return spec.width * page_size * element_bytes
+
+    def allocate(self, spec: PagedLatent, layers, num_pages, page_size, dtype, device):
+        return torch.empty((layers, num_pages, 1, page_size, spec.width), dtype=dtype, device=device)
+
+    def layer_cache(self, storage, index, group):
+        if storage is None:
+            return LayerCache(group, True)
+        return LayerCache(group, True, storage[index], storage[index], None, storage[index])
+
+
 class FixedStateKind(CacheKind):
     paged = False
 
@@ -141,4 +158,5 @@ def cache_kind(spec) -> CacheKind:
 
 
 register_cache_kind(PagedKV, PagedKVKind())
+register_cache_kind(PagedLatent, PagedLatentKind())
 register_cache_kind(FixedState, FixedStateKind())

@@ -432,3 +432,165 @@ class BuvuzenConfig(ModelConfig):
             raise ConfigError("Buvuzen configuration: " + "; ".join(faults))
         for i in range(n):
             self.weights_layer(i)
+
+
+@dataclass(frozen=True)
+class KapuvikConfig(ModelConfig):
+    """Kapuvik: a decoder whose config.json is nested and lists its layers one by one.
+
+        architecture   "Kapuvik"
+        vocab, width, norm.eps, embedding.scale, logit_softcap
+        loop           start, stop, times: layers start .. stop-1 run `times` times in a row (optional)
+        layers[i]      type "parallel":          mixer.left (heads, kv_heads, dim, vdim, scale, softcap, rot.base, rot.dims),
+                                                 mixer.right (heads, dim, vdim, decay per head, rot.base, rot.dims),
+                                                 mixer.left_scale, mixer.right_scale
+                       type "latent_attention":  mixer (heads, dim, rot_dim, vdim, kv_rank, scale, rot.base)
+                       type "gla":               mixer (heads, dim, vdim, tau; optional rank: the middle width of the decay's
+                                                 projection, otherwise read off the weight file)
+                       mlp: null | kind "dense" (ff, limit)
+
+    Every size and constant is read from there; the layers may differ from one another.  Absent optional keys mean
+    "not there": no loop, no rotation, no cap, multipliers of 1."""
+
+    architecture: ClassVar[str] = "Kapuvik"
+    model_type: ClassVar[str] = "kapuvik"
+    LAYER_TYPES: ClassVar[Tuple[str, ...]] = ("parallel", "latent_attention", "gla")
+
+    vocab: int = _field(int)
+    width: int = _field(int)
+    norm_eps: float = _field(float)
+    embedding_scale: float = _field(float, default=1.0)
+    logit_softcap: float = _field(float, default=0.0)
+    loop_start: int = _field(int, default=0)
+    loop_stop: int = _field(int, default=0)
+    loop_times: int = _field(int, default=1)
+    layers: Tuple[Dict[str, Any], ...] = _field(tuple, default=())
+
+    @classmethod
+    def from_dict(cls, raw: Dict[str, Any]) -> "KapuvikConfig":
+        faults: list = []
+
+        def get(d, path, kind, default=dataclasses.MISSING):
+            cur = d
+            for key in path.split("."):
+                if not isinstance(cur, dict) or cur.get(key) is None:
+                    if default is dataclasses.MISSING:
+                        faults.append("missing key %r" % path)
+                    return None if default is dataclasses.MISSING else default
+                cur = cur[key]
+            return _typed(path, cur, kind, faults)
+
+        values = dict(vocab=get(raw, "vocab", int), width=get(raw, "width", int), norm_eps=get(raw, "norm.eps", float),
+                      embedding_scale=get(raw, "embedding.scale", float, 1.0), logit_softcap=get(raw, "logit_softcap", float, 0.0))
+        if raw.get("loop") is not None:
+            values.update(loop_start=get(raw, "loop.start", int), loop_stop=get(raw, "loop.stop", int),
+                          loop_times=get(raw, "loop.times", int))
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            faults.append("key 'layers': expected a list of layers")
+            layers = []
+        if faults:
+            raise ConfigError("config.json for %s: %s" % (cls.__name__, "; ".join(faults)))
+        cfg = cls(layers=tuple(json.loads(json.dumps(layer)) for layer in layers), **values)
+        cfg.validate()
+        return cfg
+
+    @property
+    def looped(self) -> bool:
+        return self.loop_stop > self.loop_start
+
+    def to_dict(self) -> Dict[str, Any]:
+        out = {"architecture": self.architecture, "embedding": {"scale": self.embedding_scale},
+               "layers": json.loads(json.dumps(list(self.layers))), "logit_softcap": self.logit_softcap,
+               "norm": {"eps": self.norm_eps}, "vocab": self.vocab, "width": self.width}
+        if self.looped:
+            out["loop"] = {"start": self.loop_start, "stop": self.loop_stop, "times": self.loop_times}
+        return out
+
+    def validate(self) -> None:
+        faults = []
+
+        def positive(where, d, *keys):
+            ok = True
+            for k in keys:
+                v = d.get(k) if isinstance(d, dict) else None
+                if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+                    faults.append("%s.%s must be a positive integer, got %r" % (where, k, v))
+                    ok = False
+            return ok
+
+        def number(where, d, key, least=None, required=True):
+            v = d.get(key) if isinstance(d, dict) else None
+            if v is None and not required:
+                return True
+            if not isinstance(v, (int, float)) or isinstance(v, bool) or (least is not None and not v > least):
+                faults.append("%s.%s must be a number%s, got %r" % (where, key, "" if least is None else " above %g" % least, v))
+                return False
+            return True
+
+        def rotation(where, d, dim):
+            rot = d.get("rot") if isinstance(d, dict) else None
+            if rot is None:
+                return
+            if positive(where + ".rot", rot, "dims") and number(where + ".rot", rot, "base", 0):
+                if rot["dims"] % 2 or rot["dims"] > dim:
+                    faults.append("%s.rot.dims (%d) must be even and within the head's %d channels" % (where, rot["dims"], dim))
+
+        for name in ("vocab", "width"):
+            if getattr(self, name) <= 0:
+                faults.append("%s must be positive, got %d" % (name, getattr(self, name)))
+        if not self.norm_eps > 0:
+            faults.append("norm.eps must be positive, got %r" % self.norm_eps)
+        if self.logit_softcap < 0:
+            faults.append("logit_softcap must not be negative, got %r" % self.logit_softcap)
+        n = len(self.layers)
+        if self.loop_stop or self.loop_start or self.loop_times != 1:
+            if not (0 <= self.loop_start < self.loop_stop <= n) or self.loop_times < 1:
+                faults.append("loop: start %d, stop %d, times %d do not name a run of the %d layers at least once"
+                              % (self.loop_start, self.loop_stop, self.loop_times, n))
+        for i, layer in enumerate(self.layers):
+            at = "layers[%d]" % i
+            if not isinstance(layer, dict) or layer.get("type") not in self.LAYER_TYPES:
+                faults.append("%s.type %r is not one of %s" % (at, layer.get("type") if isinstance(layer, dict) else layer,
+                                                               list(self.LAYER_TYPES)))
+                continue
+            m, kind = layer.get("mixer"), layer["type"]
+            if kind == "parallel":
+                left, right = (m or {}).get("left"), (m or {}).get("right")
+                if positive(at + ".mixer.left", left, "heads", "kv_heads", "dim", "vdim"):
+                    if left["heads"] % left["kv_heads"]:
+                        faults.append("%s.mixer.left: heads (%d) is not a multiple of kv_heads (%d)" % (at, left["heads"], left["kv_heads"]))
+                    number(at + ".mixer.left", left, "scale")
+                    number(at + ".mixer.left", left, "softcap", 0, required=False)
+                    rotation(at + ".mixer.left", left, left["dim"])
+                if positive(at + ".mixer.right", right, "heads", "dim", "vdim"):
+                    decay = right.get("decay")
+                    if not isinstance(decay, list) or len(decay) != right["heads"] or \
+                            not all(isinstance(d, (int, float)) and not isinstance(d, bool) for d in decay):
+                        faults.append("%s.mixer.right.decay must list one number per head" % at)
+                    rotation(at + ".mixer.right", right, right["dim"])
+                number(at + ".mixer", m, "left_scale", required=False)
+                number(at + ".mixer", m, "right_scale", required=False)
+            elif kind == "latent_attention":
+                if positive(at + ".mixer", m, "heads", "dim", "rot_dim", "vdim", "kv_rank"):
+                    number(at + ".mixer", m, "scale")
+                    if m["rot_dim"] % 2:
+                        faults.append("%s.mixer.rot_dim (%d) must be even" % (at, m["rot_dim"]))
+                    if not isinstance(m.get("rot"), dict) or not number(at + ".mixer.rot", m.get("rot"), "base", 0):
+                        pass
+                    elif m["rot"].get("dims", m["rot_dim"]) != m["rot_dim"]:
+                        faults.append("%s.mixer.rot.dims must equal rot_dim" % at)
+            else:
+                if positive(at + ".mixer", m, "heads", "dim", "vdim"):
+                    number(at + ".mixer", m, "tau", 0)
+                    if m.get("rank") is not None:
+                        positive(at + ".mixer", m, "rank")
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
+                faults.append("%s.mlp.kind %r is not 'dense'" % (at, mlp.get("kind") if isinstance(mlp, dict) else mlp))
+            elif positive(at + ".mlp", mlp, "ff"):
+                number(at + ".mlp", mlp, "limit", 0)
+        if faults:
+            raise ConfigError("Kapuvik configuration: " + "; ".join(faults))

@@ -14,7 +14,10 @@
 // With `sinks` (a float32 per query head) the softmax's denominator also holds
 // exp(sinks[h]): an entry without a key or a value, not scaled.  With gate_col >= 0
 // head h's output is multiplied by sigmoid(g), g the element at column gate_col + h
-// of the token's row of `q`.
+// of the token's row of `q`.  With softcap c > 0 a scaled score s becomes c tanh(s / c) before
+// anything else is done to it.  A value row starts every v_stride elements (Dv unless the caller
+// says otherwise: a pool whose rows hold the value as the first Dv elements of the key, v_pool =
+// k_pool and v_stride = D, is read as it lies).
 //
 // Each warp takes chunks of 32 keys (chunk c goes to warp c mod 4), one key per
 // lane: the lane forms the whole dot product q.k in float32, the warp keeps a
@@ -34,7 +37,7 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
     int out_row_stride, float scale, int window, int H, int Hk, int D, int S, int Dv, int keep_first,
-    float bias_exp, const float* __restrict__ sinks, int gate_col) {
+    float bias_exp, const float* __restrict__ sinks, int gate_col, float softcap, int v_stride) {
     pdl_wait();
     pdl_trigger();
     __shared__ float q_s[ATT_MAX_D];
@@ -75,7 +78,9 @@ __global__ void paged_attention_generic_kernel(
             const T* kp = k_pool + base * D;
             float dot = 0.f;
             for (int d = 0; d < D; ++d) dot += q_s[d] * to_f32(kp[d]);
-            s = dot * scale - slope * (float)(kv_len - 1 - j);
+            s = dot * scale;
+            if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+            s -= slope * (float)(kv_len - 1 - j);
         }
         const float m_new = fmaxf(m, warp_max(s));
         const float p = valid ? expf(s - m_new) : 0.f;
@@ -87,7 +92,7 @@ __global__ void paged_attention_generic_kernel(
         for (int jj = 0; jj < nvalid; ++jj) {
             const float pj = __shfl_sync(0xffffffffu, p, jj);
             const size_t bj = __shfl_sync(0xffffffffu, (unsigned long long)base, jj);
-            const T* vp = v_pool + bj * Dv;
+            const T* vp = v_pool + bj * v_stride;
 #pragma unroll
             for (int i = 0; i < NR; ++i) {
                 const int d = lane + 32 * i;
@@ -132,26 +137,40 @@ __global__ void paged_attention_generic_kernel(
     }
 }
 
-extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const void* k_pool,
-                                          const void* v_pool, const int* block_table, int max_blocks,
-                                          const int* seq_of_token, const int* positions, void* out,
-                                          int out_row_stride, float scale, int window, int tokens,
-                                          int H, int Hk, int D, int S, int dtype, int Dv, int keep_first,
-                                          float bias_exp, const float* sinks, int gate_col, cudaStream_t stream) {
+extern "C" int vx_paged_attention_generic_cap(const void* q, int q_row_stride, const void* k_pool,
+                                              const void* v_pool, const int* block_table, int max_blocks,
+                                              const int* seq_of_token, const int* positions, void* out,
+                                              int out_row_stride, float scale, int window, int tokens,
+                                              int H, int Hk, int D, int S, int dtype, int Dv, int keep_first,
+                                              float bias_exp, const float* sinks, int gate_col, float softcap,
+                                              int v_stride, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (Dv <= 0) Dv = D;
+    if (v_stride <= 0) v_stride = Dv;
+    if (v_stride < Dv || softcap < 0.f) return VX_ERR_SHAPE;
     if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || Dv > ATT_MAX_D || S <= 0 || max_blocks <= 0)
         return VX_ERR_SHAPE;
     if (window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
     dim3 grid(tokens, H);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<float>), grid, ATT_WARPS * 32, 0, stream, (const float*)q, q_row_stride, (const float*)k_pool, (const float*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col);
+            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col, softcap, v_stride);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, (const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col);
+            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col, softcap, v_stride);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
     return VX_OK;
+}
+
+extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const void* k_pool,
+                                          const void* v_pool, const int* block_table, int max_blocks,
+                                          const int* seq_of_token, const int* positions, void* out,
+                                          int out_row_stride, float scale, int window, int tokens,
+                                          int H, int Hk, int D, int S, int dtype, int Dv, int keep_first,
+                                          float bias_exp, const float* sinks, int gate_col, cudaStream_t stream) {
+    return vx_paged_attention_generic_cap(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions,
+                                          out, out_row_stride, scale, window, tokens, H, Hk, D, S, dtype, Dv, keep_first,
+                                          bias_exp, sinks, gate_col, 0.f, 0, stream);
 }

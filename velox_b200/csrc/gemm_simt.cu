@@ -14,9 +14,13 @@
 template <typename TA, typename TC>
 __global__ void __launch_bounds__(256)
 gemm_nt_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const float* __restrict__ bias,
-                    TC* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
+                    TC* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc, long long sa, long long sw,
+                    long long sc) {
     pdl_wait();
     pdl_trigger();
+    A += (size_t)blockIdx.z * sa;   // (a batch of products: member z has its own A, W and C, no bias)
+    W += (size_t)blockIdx.z * sw;
+    C += (size_t)blockIdx.z * sc;
     __shared__ float As[GS_BK][GS_BM + 1];
     __shared__ float Ws[GS_BK][GS_BN + 1];
     const int tid = threadIdx.x;
@@ -70,21 +74,28 @@ gemm_nt_simt_kernel(const TA* __restrict__ A, const TA* __restrict__ W, const fl
 }
 
 // in_dtype: element type of A and W; out_dtype: element type of C.
-extern "C" int vx_gemm_nt_simt(const void* A, const void* W, const float* bias, void* C, int M, int N,
-                               int K, int lda, int ldw, int ldc, int in_dtype, int out_dtype,
-                               cudaStream_t stream) {
-    if (M <= 0 || N <= 0) return VX_OK;
+// A batch of `batch` products: member z reads A + z sa, W + z sw and writes C + z sc (strides in elements).
+extern "C" int vx_gemm_nt_simt_batched(const void* A, const void* W, const float* bias, void* C, int M, int N,
+                                       int K, int lda, int ldw, int ldc, int batch, long long sa, long long sw,
+                                       long long sc, int in_dtype, int out_dtype, cudaStream_t stream) {
+    if (M <= 0 || N <= 0 || batch <= 0) return VX_OK;
     if (K <= 0 || lda < K || ldw < K || ldc < N) return VX_ERR_SHAPE;
-    dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM);
-    if (grid.y > 65535) return VX_ERR_LIMIT;
+    dim3 grid((N + GS_BN - 1) / GS_BN, (M + GS_BM - 1) / GS_BM, batch);
+    if (grid.y > 65535 || batch > 65535) return VX_ERR_LIMIT;
     if (in_dtype == VX_F32 && out_dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<float, float>), grid, 256, 0, stream, (const float*)A, (const float*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
+        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<float, float>), grid, 256, 0, stream, (const float*)A, (const float*)W, bias, (float*)C, M, N, K, lda, ldw, ldc, sa, sw, sc);
     else if (in_dtype == VX_BF16 && out_dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<bf16, bf16>), grid, 256, 0, stream, (const bf16*)A, (const bf16*)W, bias, (bf16*)C, M, N, K, lda, ldw, ldc);
+        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<bf16, bf16>), grid, 256, 0, stream, (const bf16*)A, (const bf16*)W, bias, (bf16*)C, M, N, K, lda, ldw, ldc, sa, sw, sc);
     else if (in_dtype == VX_BF16 && out_dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<bf16, float>), grid, 256, 0, stream, (const bf16*)A, (const bf16*)W, bias, (float*)C, M, N, K, lda, ldw, ldc);
+        VX_LAUNCH_K(VX_K_GEMM, (gemm_nt_simt_kernel<bf16, float>), grid, 256, 0, stream, (const bf16*)A, (const bf16*)W, bias, (float*)C, M, N, K, lda, ldw, ldc, sa, sw, sc);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
     return VX_OK;
+}
+
+extern "C" int vx_gemm_nt_simt(const void* A, const void* W, const float* bias, void* C, int M, int N,
+                               int K, int lda, int ldw, int ldc, int in_dtype, int out_dtype,
+                               cudaStream_t stream) {
+    return vx_gemm_nt_simt_batched(A, W, bias, C, M, N, K, lda, ldw, ldc, 1, 0, 0, 0, in_dtype, out_dtype, stream);
 }

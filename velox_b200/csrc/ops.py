@@ -95,6 +95,15 @@ def _declare(lib) -> None:
         "vx_paged_prefill_attention": [P, I, P, P, P, I, P, P, P, P, I, F, I, I, I, I, I, I, I, P],
         "vx_paged_decode_attention": [P, I, P, P, P, I, P, P, P, P, I, P, I, F, I, I, I, I, I, I, I, I, P],
         "vx_sample": [P, I, I, I, P, P, P, P, P],
+        "vx_qk_norm_rope_kv_pairs": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, I, P],
+        "vx_paged_attention_generic_cap": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P, I, F, I, P],
+        "vx_gemm_nt_simt_batched": [P, P, P, P, I, I, I, I, I, I, I, c_longlong, c_longlong, c_longlong, I, I, P],
+        "vx_linear_attention_walk": [P, I, I, I, I, P, P, I, F, P, I, I, P, F, F, P, P, P, P, I, I, I, I, I, P],
+        "vx_head_norm_gate": [P, P, I, P, P, I, I, I, F, I, I, P],
+        "vx_latent_prep": [P, I, P, I, P, P, F, P, I, P, P, P, I, I, I, I, I, I, P],
+        "vx_capped_gated_act": [P, P, P, I, I, F, F, I, P],
+        "vx_sum_add_rmsnorm": [P, P, F, P, F, P, F, P, P, P, P, I, I, F, I, P],
+        "vx_softcap_rows": [P, P, c_longlong, F, P],
     }
     lib.vx_set_pdl_mask.argtypes = [I]
     lib.vx_set_pdl_mask.restype = None
@@ -245,10 +254,11 @@ def gated_act(gate_up: torch.Tensor, activation: str, block: int = 0,
 
 def qk_norm_rope_kv(qkv: torch.Tensor, q_weight, k_weight, eps: float, inv_freq, rot_dim: int,
                     positions: torch.Tensor, slot_mapping, k_pool, v_pool, num_heads: int, num_kv_heads: int,
-                    head_dim: int, v_head_dim: int = 0) -> None:
+                    head_dim: int, v_head_dim: int = 0, interleaved: bool = False) -> None:
     """In place on the packed projections `qkv` [T, (H+Hk)D + Hk Dv (+ more)]; writes new keys
     and values into the pools [pages, Hk, S, D] and [pages, Hk, S, Dv] when a slot mapping is given
-    (`v_head_dim` 0: values of the keys' size)."""
+    (`v_head_dim` 0: values of the keys' size).  The rotation pairs channel i with i + rot_dim/2, or, when
+    `interleaved`, channel 2i with 2i + 1."""
     v_head_dim = int(v_head_dim) or head_dim
     _dev(qkv, q_weight, k_weight, inv_freq, positions, slot_mapping, k_pool, v_pool)
     _need(qkv.is_contiguous() and positions.dtype == torch.int32, "qk_norm_rope_kv: contiguous qkv, int32 positions")
@@ -264,10 +274,10 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_weight, k_weight, eps: float, inv_freq,
     for w in (q_weight, k_weight):
         if w is not None:
             _need(w.dtype == torch.float32 and w.numel() == head_dim, "qk_norm_rope_kv: norm weight size")
-    _check(library().vx_qk_norm_rope_kv(
+    _check(library().vx_qk_norm_rope_kv_pairs(
         _ptr(qkv), qkv.shape[-1], _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), int(rot_dim),
         _ptr(positions), _ptr(slot_mapping), _ptr(k_pool), _ptr(v_pool), qkv.shape[0], num_heads, num_kv_heads,
-        head_dim, page_size, dtype_code(qkv.dtype), v_head_dim, _stream()), "qk_norm_rope_kv")
+        head_dim, page_size, dtype_code(qkv.dtype), v_head_dim, 1 if interleaved else 0, _stream()), "qk_norm_rope_kv")
 
 
 ATTENTION_MAX_HEAD_DIM = 256
@@ -283,26 +293,29 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
                             seq_of_token, positions, scale: float, window: int, num_heads: int,
                             num_kv_heads: int, head_dim: int, tokens: int, v_head_dim: int = 0, keep_first: int = 0,
                             bias_exponent: float = 0.0, sinks: Optional[torch.Tensor] = None,
-                            gate_col: int = -1) -> torch.Tensor:
+                            gate_col: int = -1, softcap: float = 0.0, v_stride: int = 0) -> torch.Tensor:
     """The general kernel.  `v_head_dim`: size of a value (0: a key's); `keep_first`: with a window, the
     first positions that stay visible; `bias_exponent` b > 0: head h's scores lose
     2^(-b (h + 1) / heads) * distance; `sinks` (float32 per head): the softmax's denominator also holds
-    exp(sink); `gate_col` >= 0: head h's output times sigmoid of column gate_col + h of the token's row of `q`."""
+    exp(sink); `gate_col` >= 0: head h's output times sigmoid of column gate_col + h of the token's row of `q`;
+    `softcap` c > 0: a scaled score s becomes c tanh(s / c); `v_stride`: elements from one value row of
+    `v_pool` to the next (0: v_head_dim), for a pool whose rows hold the value inside the key's row."""
     _dev(q, k_pool, v_pool, block_table, seq_of_token, positions, sinks)
     _check_sinks_gate("paged_attention", sinks, gate_col, num_heads, q_row_stride)
     v_head_dim = int(v_head_dim) or head_dim
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
           "paged_attention: int32 block table [requests, blocks]")
     _need(k_pool.dtype == q.dtype and v_pool.dtype == q.dtype, "paged_attention: pools of the queries' element type")
+    page_size = k_pool.shape[-2]
     _need(0 < head_dim <= ATTENTION_MAX_HEAD_DIM and 0 < v_head_dim <= ATTENTION_MAX_HEAD_DIM,
           "paged_attention: head sizes %d / %d (the general kernel takes sizes up to %d)"
           % (head_dim, v_head_dim, ATTENTION_MAX_HEAD_DIM))
     out = torch.empty((tokens, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
-    _check(library().vx_paged_attention_generic(
+    _check(library().vx_paged_attention_generic_cap(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
         _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale), int(window), tokens,
-        num_heads, num_kv_heads, head_dim, k_pool.shape[2], dtype_code(q.dtype), v_head_dim, int(keep_first),
-        float(bias_exponent), _ptr(sinks), int(gate_col), _stream()), "paged_attention_generic")
+        num_heads, num_kv_heads, head_dim, page_size, dtype_code(q.dtype), v_head_dim, int(keep_first),
+        float(bias_exponent), _ptr(sinks), int(gate_col), float(softcap), int(v_stride), _stream()), "paged_attention_generic")
     return out
 
 
@@ -848,6 +861,139 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optiona
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     _check(library().vx_gemm_nt_simt(_ptr(a), _ptr(w), _ptr(bias), _ptr(out), m, n, k, a.stride(0), w.stride(0), n,
                                      dtype_code(a.dtype), dtype_code(out_dtype), _stream()), "gemm_nt_simt")
+    return out
+
+
+def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One product per head: out[:, h, :] = a[:, h, :] w[h]^T with a [M, H, K], w [H, N, K] (contiguous), out [M, H, N];
+    `a` and `out` may be views into wider rows (their last dimension contiguous).  float32 multiply-adds."""
+    _dev(a, w, out)
+    _need(a.dim() == 3 and w.dim() == 3 and out.dim() == 3 and w.is_contiguous() and a.shape[1] == w.shape[0]
+          and a.shape[2] == w.shape[2] and out.shape == (a.shape[0], w.shape[0], w.shape[1]), "gemm_heads: a [M,H,K], w [H,N,K], out [M,H,N]")
+    _need(a.stride(2) == 1 and out.stride(2) == 1 and a.dtype == w.dtype, "gemm_heads: rows contiguous, one element type")
+    m, h, k = a.shape
+    n = w.shape[1]
+    _check(library().vx_gemm_nt_simt_batched(_ptr(a), _ptr(w), None, _ptr(out), m, n, k, a.stride(0), k, out.stride(0), h,
+                                             a.stride(1), n * k, out.stride(1), dtype_code(a.dtype), dtype_code(out.dtype),
+                                             _stream()), "gemm_nt_simt_heads")
+    return out
+
+
+def linear_attention_walk(x: torch.Tensor, q_col: int, k_col: int, v_col: int, state: torch.Tensor, cu_seqlens, state_slots,
+                          seqs: int, heads: int, dim: int, vdim: int, decay: Optional[torch.Tensor] = None,
+                          gate: Optional[torch.Tensor] = None, gate_mul: float = 1.0, inv_freq: Optional[torch.Tensor] = None,
+                          rot_dim: int = 0, interleaved: bool = False, positions: Optional[torch.Tensor] = None,
+                          q_mul: float = 1.0, k_mul: float = 1.0) -> torch.Tensor:
+    """Per head S = a (.) S + k v^T, o = S^T q over every request's tokens in order, a = decay[h] (float32 per head) or
+    sigmoid(gate)^gate_mul per key channel and token (`gate` float32 [tokens, heads * dim], contiguous rows).  q and k
+    are turned by position * inv_freq on their first `rot_dim` channels, then multiplied by q_mul / k_mul, all in
+    float32.  `state` float32 [slots, heads, dim, vdim] is read and written back.  Returns float32 [tokens, heads * vdim]."""
+    _dev(x, decay, gate, inv_freq, positions, state, cu_seqlens, state_slots)
+    _need(x.stride(1) == 1 and (decay is None) != (gate is None), "linear_attention_walk: a decay per head or a gate per channel")
+    if decay is not None:
+        _need(decay.dtype == torch.float32 and decay.numel() == heads, "linear_attention_walk: float32 decay per head")
+    if gate is not None:
+        _need(gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == (x.shape[0], heads * dim),
+              "linear_attention_walk: float32 gate [tokens, heads * dim]")
+    if inv_freq is not None:
+        _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dim and positions is not None
+              and positions.dtype == torch.int32, "linear_attention_walk: inv_freq of rot_dim / 2 numbers, int32 positions")
+    _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
+          "linear_attention_walk: float32 state [slots, heads, dim, vdim]")
+    out = torch.empty((x.shape[0], heads * vdim), dtype=torch.float32, device=x.device)
+    _check(library().vx_linear_attention_walk(
+        _ptr(x), x.stride(0), int(q_col), int(k_col), int(v_col), _ptr(decay), _ptr(gate), gate.stride(0) if gate is not None else 0,
+        float(gate_mul), _ptr(inv_freq), int(rot_dim) if inv_freq is not None else 0, 1 if interleaved else 0, _ptr(positions),
+        float(q_mul), float(k_mul), _ptr(state), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out), int(seqs), heads, dim, vdim,
+        dtype_code(x.dtype), _stream()), "linear_attention_walk")
+    return out
+
+
+def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], heads: int, eps: float,
+                   gate_activation: str = "silu") -> torch.Tensor:
+    """Every head of o (float32 [rows, heads * vdim]) divided by its root mean square, times `weight` [vdim] if given,
+    times silu or sigmoid of `gate` [rows, heads * vdim] (contiguous rows); in the gate's element type."""
+    _dev(o, gate, weight)
+    vdim = o.shape[1] // heads
+    _need(o.dtype == torch.float32 and o.is_contiguous() and gate.stride(1) == 1 and gate.shape == o.shape
+          and o.shape[1] == heads * vdim, "head_norm_gate: float32 outputs and a gate of their shape")
+    _need(weight is None or (weight.dtype == torch.float32 and weight.numel() == vdim), "head_norm_gate: float32 weight [vdim]")
+    _need(gate_activation in ("silu", "sigmoid"), "head_norm_gate: the gate passes through silu or sigmoid")
+    out = torch.empty(o.shape, dtype=gate.dtype, device=o.device)
+    _check(library().vx_head_norm_gate(_ptr(o), _ptr(gate), gate.stride(0), _ptr(weight), _ptr(out), o.shape[0], heads, vdim,
+                                       float(eps), 1 if gate_activation == "silu" else 0, dtype_code(gate.dtype), _stream()),
+           "head_norm_gate")
+    return out
+
+
+def latent_prep(down: torch.Tensor, q: torch.Tensor, qa: torch.Tensor, weight: torch.Tensor, eps: float, inv_freq: torch.Tensor,
+                interleaved: bool, positions: torch.Tensor, slot_mapping, pool, heads: int, dim: int, rot_dim: int,
+                rank: int) -> None:
+    """`down` [T, rank + rot_dim]: the first `rank` channels RMS-normed with `weight` and, followed by the rotated last
+    `rot_dim`, written to `pool` (rows of rank + rot_dim elements) at the step's slots; the last rot_dim channels of every
+    head of `q` [T, heads * (dim + rot_dim)] rotated into the last rot_dim channels of `qa` [T, heads, rank + rot_dim]."""
+    _dev(down, q, qa, weight, inv_freq, positions, slot_mapping, pool)
+    _need(qa.is_contiguous() and qa.dtype == q.dtype and tuple(qa.shape) == (q.shape[0], heads, rank + rot_dim),
+          "latent_prep: folded queries [T, heads, rank + rot_dim]")
+    _need(down.stride(1) == 1 and q.stride(1) == 1 and down.dtype == q.dtype and positions.dtype == torch.int32,
+          "latent_prep: rows contiguous, one element type, int32 positions")
+    _need(weight.dtype == torch.float32 and weight.numel() == rank and inv_freq.dtype == torch.float32
+          and inv_freq.numel() * 2 == rot_dim, "latent_prep: float32 weight [rank] and rot_dim / 2 frequencies")
+    if slot_mapping is not None:
+        _need(pool is not None and pool.dtype == q.dtype and pool.is_contiguous() and pool.shape[-1] == rank + rot_dim,
+              "latent_prep: a pool of rows of rank + rot_dim elements")
+    _check(library().vx_latent_prep(_ptr(down), down.stride(0), _ptr(q), q.stride(0), _ptr(qa), _ptr(weight), float(eps), _ptr(inv_freq),
+                                    1 if interleaved else 0, _ptr(positions), _ptr(slot_mapping), _ptr(pool), q.shape[0],
+                                    heads, dim, rot_dim, rank, dtype_code(q.dtype), _stream()), "latent_prep")
+
+
+def capped_gated_act(sums: torch.Tensor, bias: Optional[torch.Tensor], limit: float, slope: float,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """sums float32 [rows, 2 inner] (all gates, then all ups), `bias` float32 [2 inner] added first:
+    g = min(gate, limit), u = clamp(up, -limit, limit); g sigmoid(slope g) (u + 1), rounded once to `out_dtype`."""
+    _dev(sums, bias)
+    _need(sums.dtype == torch.float32 and sums.is_contiguous() and sums.dim() == 2 and sums.shape[1] % 2 == 0,
+          "capped_gated_act: float32 rows of even width")
+    inner = sums.shape[1] // 2
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == 2 * inner), "capped_gated_act: float32 bias")
+    out = torch.empty((sums.shape[0], inner), dtype=out_dtype, device=sums.device)
+    _check(library().vx_capped_gated_act(_ptr(sums), _ptr(bias), _ptr(out), sums.shape[0], inner, float(limit), float(slope),
+                                         dtype_code(out_dtype), _stream()), "capped_gated_act")
+    return out
+
+
+def sum_add_rmsnorm(residual: torch.Tensor, branches=(), rows_add: Optional[torch.Tensor] = None,
+                    vec: Optional[torch.Tensor] = None, weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+                    out_dtype: Optional[torch.dtype] = None) -> Optional[torch.Tensor]:
+    """residual (float32, in place) += sum of c * y over up to three `branches` [(y, c)] + rows_add (float32, the
+    residual's shape) + vec (float32 [width]); with `weight` returns rmsnorm(residual) * weight in `out_dtype`."""
+    branches = [(y, c) for y, c in branches if y is not None]
+    _dev(residual, rows_add, vec, weight, *[y for y, _ in branches])
+    _need(residual.dtype == torch.float32 and residual.is_contiguous() and len(branches) <= 3, "sum_add_rmsnorm: float32 residual")
+    width = residual.shape[-1]
+    dt = branches[0][0].dtype if branches else (out_dtype or torch.float32)
+    for y, _ in branches:
+        _need(y.dtype == dt and y.is_contiguous() and y.shape == residual.shape, "sum_add_rmsnorm: branches of the residual's shape")
+    _need(rows_add is None or (rows_add.dtype == torch.float32 and rows_add.is_contiguous() and rows_add.shape == residual.shape),
+          "sum_add_rmsnorm: float32 rows of the residual's shape")
+    for v in (vec, weight):
+        _need(v is None or (v.dtype == torch.float32 and v.numel() == width and v.is_contiguous()), "sum_add_rmsnorm: float32 vectors of the row's width")
+    if out_dtype is not None and branches:
+        _need(out_dtype == dt, "sum_add_rmsnorm: the normed rows have the branches' element type")
+    out = torch.empty(residual.shape, dtype=dt, device=residual.device) if weight is not None else None
+    b = branches + [(None, 0.0)] * (3 - len(branches))
+    _check(library().vx_sum_add_rmsnorm(_ptr(residual), _ptr(b[0][0]), float(b[0][1]), _ptr(b[1][0]), float(b[1][1]), _ptr(b[2][0]),
+                                        float(b[2][1]), _ptr(rows_add), _ptr(vec), _ptr(weight), _ptr(out), residual.shape[0],
+                                        width, float(eps), dtype_code(dt), _stream()), "sum_add_rmsnorm")
+    return out
+
+
+def softcap_rows(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """cap * tanh(x / cap) on float32 x."""
+    _dev(x)
+    _need(x.dtype == torch.float32 and x.is_contiguous(), "softcap_rows: float32 rows")
+    out = torch.empty_like(x)
+    _check(library().vx_softcap_rows(_ptr(x), _ptr(out), x.numel(), float(cap), _stream()), "softcap_rows")
     return out
 
 

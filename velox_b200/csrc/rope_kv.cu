@@ -8,8 +8,9 @@
 // One warp handles one head of one token:
 //   q, k:  x = x * rsqrt(mean(x^2) + eps) * w[d]          (if a weight is given)
 //          pairs (i, i + rot/2), i < rot/2, rotated by angle = pos * inv_freq[i]
-//          (half-split convention; angle, sine and cosine in float32, computed
-//          here rather than read from a table rounded to the element type)
+//          (half-split convention; with `interleaved` the pairs are (2i, 2i + 1) instead;
+//          angle, sine and cosine in float32, computed here rather than read from a
+//          table rounded to the element type)
 //   q is written back in place; k goes to k_pool, v (untouched) to v_pool at
 //   slot_mapping[token] = page * S + offset, pools laid out [page, Hk, S, D] and [page, Hk, S, Dv].
 // A token whose slot is negative writes nothing.  Without a slot mapping (a layer
@@ -27,7 +28,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
                                        const float* __restrict__ inv_freq, int rot_dim,
                                        const int* __restrict__ positions,
                                        const int* __restrict__ slot_mapping, T* __restrict__ k_pool,
-                                       T* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv) {
+                                       T* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv, int interleaved) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float smem[];
@@ -69,9 +70,10 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
         for (int i = lane; i < half; i += 32) {
             float sn, cs;
             sincosf(pos * inv_freq[i], &sn, &cs);
-            const float a = buf[i], b = buf[i + half];
-            buf[i] = a * cs - b * sn;
-            buf[i + half] = a * sn + b * cs;
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            const float a = buf[ia], b = buf[ib];
+            buf[ia] = a * cs - b * sn;
+            buf[ib] = a * sn + b * cs;
         }
         __syncwarp();
     }
@@ -218,18 +220,19 @@ qk_norm_rope_kv_128_row_kernel(bf16* __restrict__ qkv, int row_stride, const flo
     }
 }
 
-extern "C" int vx_qk_norm_rope_kv(void* qkv, int row_stride, const float* q_weight,
-                                  const float* k_weight, float eps, const float* inv_freq,
-                                  int rot_dim, const int* positions, const int* slot_mapping,
-                                  void* k_pool, void* v_pool, int tokens, int H, int Hk, int D, int S,
-                                  int dtype, int Dv, cudaStream_t stream) {
+extern "C" int vx_qk_norm_rope_kv_pairs(void* qkv, int row_stride, const float* q_weight,
+                                        const float* k_weight, float eps, const float* inv_freq,
+                                        int rot_dim, const int* positions, const int* slot_mapping,
+                                        void* k_pool, void* v_pool, int tokens, int H, int Hk, int D, int S,
+                                        int dtype, int Dv, int interleaved, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (Dv <= 0) Dv = D;
     if (H <= 0 || Hk <= 0 || D <= 0 || S <= 0 || D > ROPE_MAX_D || Dv > ROPE_MAX_D) return VX_ERR_SHAPE;
     if (rot_dim < 0 || rot_dim > D || (rot_dim & 1)) return VX_ERR_SHAPE;
     if (row_stride < (H + Hk) * D + Hk * Dv) return VX_ERR_SHAPE;
     if (slot_mapping && (!k_pool || !v_pool)) return VX_ERR_SHAPE;
-    if (dtype == VX_BF16 && D == 128 && Dv == D && (rot_dim == D || !inv_freq) && !(row_stride & 3) &&
+    if (!inv_freq || rot_dim == 0) interleaved = 0;
+    if (!interleaved && dtype == VX_BF16 && D == 128 && Dv == D && (rot_dim == D || !inv_freq) && !(row_stride & 3) &&
         !((((uintptr_t)qkv) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 7)) {
         if (tokens >= ROPE128_TOKEN_MIN) {
             VX_LAUNCH_K(VX_K_ROPE, qk_norm_rope_kv_128_row_kernel, tokens, ROPE128_WARPS * 32, 0, stream, (bf16*)qkv,
@@ -249,12 +252,22 @@ extern "C" int vx_qk_norm_rope_kv(void* qkv, int row_stride, const float* q_weig
     const size_t smem = (size_t)ROPE_WARPS * D * sizeof(float);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<float>), grid, ROPE_WARPS * 32, smem, stream, (float*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
-            (float*)k_pool, (float*)v_pool, H, Hk, D, S, Dv);
+            (float*)k_pool, (float*)v_pool, H, Hk, D, S, Dv, interleaved);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<bf16>), grid, ROPE_WARPS * 32, smem, stream, (bf16*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
-            (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S, Dv);
+            (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S, Dv, interleaved);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
     return VX_OK;
+}
+
+// The half-split rotation under its first name.
+extern "C" int vx_qk_norm_rope_kv(void* qkv, int row_stride, const float* q_weight,
+                                  const float* k_weight, float eps, const float* inv_freq,
+                                  int rot_dim, const int* positions, const int* slot_mapping,
+                                  void* k_pool, void* v_pool, int tokens, int H, int Hk, int D, int S,
+                                  int dtype, int Dv, cudaStream_t stream) {
+    return vx_qk_norm_rope_kv_pairs(qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
+                                    k_pool, v_pool, tokens, H, Hk, D, S, dtype, Dv, 0, stream);
 }

@@ -1,0 +1,374 @@
+// Kernels around mixers with a recurrent state or a latent cache, and around blocks whose
+// sublayers run side by side:
+//   linear_attention_walk   S_p = a_p (.) S_(p-1) + k_p v_p^T, o_p = S_p^T q_p with the decay a number per
+//                           head or a number per key channel and position; q and k optionally rotated by
+//                           position and multiplied by numbers on the way in
+//   head_norm_gate          every head's output divided by its root mean square (optionally times a
+//                           weight shared by the heads), times silu or sigmoid of a gate projection
+//   latent_prep             the down-projected row of a latent attention: norm of the latent part, rotation
+//                           of the shared key part, both into the page; rotation of the queries' rotated part
+//   capped_gated_act        min(g, L) sigmoid(s min(g, L)) (clamp(u, -L, L) + 1) on float32 sums plus biases
+//   sum_add_rmsnorm         residual += c0 y0 + c1 y1 + c2 y2 + rows + vector; optionally the norm of the sum
+//   softcap_rows            c tanh(x / c)
+// All statistics, sums, angles, decays and states are float32; T is the element type of
+// the activations that feed matrix products.
+#include "common.cuh"
+
+#define LW_COLS 32
+#define LW_SLICES 4
+#define LW_CHUNK 16
+#define LW_MAX_SMEM (sizeof(float) * LW_CHUNK * (3 * 256 + LW_COLS))   // D up to 256, with a gate
+
+__device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
+
+// A block owns LW_COLS columns of one head's state of one request; a thread owns every fourth row of
+// one column.  Tokens are staged LW_CHUNK at a time in shared memory, in float32: q and k as the
+// projection left them, turned by position * inv_freq[i] on the first rot_dim channels (pairs
+// (i, i + rot_dim/2), or (2i, 2i + 1) when `interleaved`), then times q_mul / k_mul.  The decay of
+// channel d at token t is decay[h] (`gate` null), or exp(gate_mul * log_sigmoid(gate[t, h D + d])):
+// sigmoid(z)^(gate_mul), formed through the logarithm.  Every sum runs in an order fixed by D alone.
+template <typename T, int DR>
+__global__ void __launch_bounds__(LW_COLS * LW_SLICES)
+linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_col, int v_col,
+                             const float* __restrict__ decay, const float* __restrict__ gate, int ldg, float gate_mul,
+                             const float* __restrict__ inv_freq, int rot_dim, int interleaved,
+                             const int* __restrict__ positions, float q_mul, float k_mul, float* __restrict__ state,
+                             const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
+                             float* __restrict__ out, int H, int D, int Dv) {
+    extern __shared__ float smem[];
+    float* q_s = smem;                       // [LW_CHUNK][D]
+    float* k_s = q_s + LW_CHUNK * D;         // [LW_CHUNK][D]
+    float* v_s = k_s + LW_CHUNK * D;         // [LW_CHUNK][LW_COLS]
+    float* a_s = v_s + LW_CHUNK * LW_COLS;   // [LW_CHUNK][D] (with a gate only)
+    const int col0 = blockIdx.x * LW_COLS, h = blockIdx.y, seq = blockIdx.z;
+    const int col = threadIdx.x / LW_SLICES, slice = threadIdx.x % LW_SLICES;
+    const int c = col0 + col;
+    const bool live = c < Dv;
+    const float dec = decay ? decay[h] : 1.f;
+    const int half = rot_dim >> 1;
+    pdl_wait();
+    pdl_trigger();
+    const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
+    float* st = state + (((size_t)state_slots[seq] * H + h) * D) * Dv;
+    float S[DR];
+#pragma unroll
+    for (int i = 0; i < DR; ++i) {
+        const int d = slice + LW_SLICES * i;
+        S[i] = (live && d < D) ? st[(size_t)d * Dv + c] : 0.f;
+    }
+    for (int tb = t0; tb < t1; tb += LW_CHUNK) {
+        const int n = min(LW_CHUNK, t1 - tb);
+        __syncthreads();
+        for (int i = threadIdx.x; i < n * D; i += blockDim.x) {
+            const int tt = i / D, d = i - tt * D;
+            const T* row = x + (size_t)(tb + tt) * ldx + (size_t)h * D + d;
+            q_s[i] = to_f32(row[q_col]);
+            k_s[i] = to_f32(row[k_col]);
+            if (gate) a_s[i] = expf(gate_mul * log_sigmoid(gate[(size_t)(tb + tt) * ldg + (size_t)h * D + d]));
+        }
+        for (int i = threadIdx.x; i < n * LW_COLS; i += blockDim.x) {
+            const int tt = i / LW_COLS, cc = i - tt * LW_COLS;
+            v_s[i] = (col0 + cc < Dv) ? to_f32(x[(size_t)(tb + tt) * ldx + v_col + (size_t)h * Dv + col0 + cc]) : 0.f;
+        }
+        __syncthreads();
+        if (inv_freq && half > 0) {
+            for (int i = threadIdx.x; i < n * half; i += blockDim.x) {
+                const int tt = i / half, p = i - tt * half;
+                float sn, cs;
+                sincosf((float)positions[tb + tt] * inv_freq[p], &sn, &cs);
+                const int ia = tt * D + (interleaved ? 2 * p : p), ib = tt * D + (interleaved ? 2 * p + 1 : p + half);
+                const float qa = q_s[ia], qb = q_s[ib], ka = k_s[ia], kb = k_s[ib];
+                q_s[ia] = qa * cs - qb * sn;
+                q_s[ib] = qb * cs + qa * sn;
+                k_s[ia] = ka * cs - kb * sn;
+                k_s[ib] = kb * cs + ka * sn;
+            }
+            __syncthreads();
+        }
+        if (q_mul != 1.f || k_mul != 1.f) {
+            for (int i = threadIdx.x; i < n * D; i += blockDim.x) { q_s[i] *= q_mul; k_s[i] *= k_mul; }
+            __syncthreads();
+        }
+        for (int tt = 0; tt < n; ++tt) {
+            const float v = v_s[tt * LW_COLS + col];
+            const float* kq = k_s + tt * D;
+            const float* qq = q_s + tt * D;
+            const float* aa = a_s + tt * D;
+            float o = 0.f;
+#pragma unroll
+            for (int i = 0; i < DR; ++i) {
+                const int d = slice + LW_SLICES * i;
+                if (d < D) {
+                    S[i] = fmaf(gate ? aa[d] : dec, S[i], kq[d] * v);
+                    o = fmaf(S[i], qq[d], o);
+                }
+            }
+            o += __shfl_xor_sync(0xffffffffu, o, 1);
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            if (slice == 0 && live) out[(size_t)(tb + tt) * H * Dv + (size_t)h * Dv + c] = o;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < DR; ++i) {
+        const int d = slice + LW_SLICES * i;
+        if (live && d < D) st[(size_t)d * Dv + c] = S[i];
+    }
+}
+
+template <typename T>
+static int launch_linear_attention_walk(const T* x, int ldx, int q_col, int k_col, int v_col, const float* decay,
+                                        const float* gate, int ldg, float gate_mul, const float* inv_freq, int rot_dim,
+                                        int interleaved, const int* positions, float q_mul, float k_mul, float* state,
+                                        const int* cu_seqlens, const int* state_slots, float* out, int seqs, int H, int D,
+                                        int Dv, cudaStream_t stream) {
+    dim3 grid((Dv + LW_COLS - 1) / LW_COLS, H, seqs);
+    const size_t smem = sizeof(float) * LW_CHUNK * ((gate ? 3 : 2) * D + LW_COLS);
+    const int dr = (D + LW_SLICES - 1) / LW_SLICES;
+    static bool configured[4][VX_MAX_DEVICES];
+#define LW_GO(DR, SLOT)                                                                                                \
+    do {                                                                                                               \
+        if (int rc = vx_configure_smem(linear_attention_walk_kernel<T, DR>, LW_MAX_SMEM, configured[SLOT])) return rc;          \
+        VX_LAUNCH_K(VX_K_ATTENTION, (linear_attention_walk_kernel<T, DR>), grid, LW_COLS * LW_SLICES, smem, stream, x,  \
+                    ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul, inv_freq, rot_dim, interleaved, positions,    \
+                    q_mul, k_mul, state, cu_seqlens, state_slots, out, H, D, Dv);                                       \
+    } while (0)
+    if (dr <= 8) LW_GO(8, 0);
+    else if (dr <= 16) LW_GO(16, 1);
+    else if (dr <= 32) LW_GO(32, 2);
+    else LW_GO(64, 3);
+#undef LW_GO
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// x: rows with q, k [H, D] and v [H, Dv] at the given columns.  decay [H] or gate [tokens, ldg] (float32; one
+// of the two).  state float32 [slot, H, D, Dv], read and written back.  out float32 [tokens, H * Dv].
+extern "C" int vx_linear_attention_walk(const void* x, int ldx, int q_col, int k_col, int v_col, const float* decay,
+                                        const float* gate, int ldg, float gate_mul, const float* inv_freq, int rot_dim,
+                                        int interleaved, const int* positions, float q_mul, float k_mul, float* state,
+                                        const int* cu_seqlens, const int* state_slots, float* out, int seqs, int H,
+                                        int D, int Dv, int dtype, cudaStream_t stream) {
+    if (seqs <= 0) return VX_OK;
+    if (H <= 0 || D <= 0 || Dv <= 0 || D > 256 || q_col < 0 || k_col < 0 || v_col < 0) return VX_ERR_SHAPE;
+    if ((decay == nullptr) == (gate == nullptr)) return VX_ERR_SHAPE;
+    if (gate && ldg < H * D) return VX_ERR_SHAPE;
+    if (rot_dim < 0 || rot_dim > D || (rot_dim & 1) || (inv_freq && rot_dim > 0 && !positions)) return VX_ERR_SHAPE;
+    if (seqs > 65535 || H > 65535) return VX_ERR_LIMIT;
+    if (dtype == VX_F32)
+        return launch_linear_attention_walk<float>((const float*)x, ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul,
+                                                   inv_freq, rot_dim, interleaved, positions, q_mul, k_mul, state,
+                                                   cu_seqlens, state_slots, out, seqs, H, D, Dv, stream);
+    if (dtype == VX_BF16)
+        return launch_linear_attention_walk<bf16>((const bf16*)x, ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul,
+                                                  inv_freq, rot_dim, interleaved, positions, q_mul, k_mul, state,
+                                                  cu_seqlens, state_slots, out, seqs, H, D, Dv, stream);
+    return VX_ERR_DTYPE;
+}
+
+// One warp per (token, head): out = o / sqrt(mean(o^2) + eps) (* w[d]) * act(g), act = sigmoid (0) or silu (1).
+template <typename T>
+__global__ void head_norm_gate_kernel(const float* __restrict__ o, const T* __restrict__ g, int ldg,
+                                      const float* __restrict__ w, T* __restrict__ out, int rows, int H, int Dv, float eps,
+                                      int gate_act) {
+    pdl_wait();
+    pdl_trigger();
+    const int unit = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (unit >= rows * H) return;
+    const int t = unit / H, h = unit - t * H;
+    const float* src = o + ((size_t)t * H + h) * Dv;
+    float ss = 0.f;
+    for (int d = lane; d < Dv; d += 32) { const float v = src[d]; ss += v * v; }
+    ss = warp_sum(ss);
+    const float rstd = rsqrtf(ss / (float)Dv + eps);
+    const T* gr = g + (size_t)t * ldg + (size_t)h * Dv;
+    T* dst = out + ((size_t)t * H + h) * Dv;
+    for (int d = lane; d < Dv; d += 32) {
+        const float z = to_f32(gr[d]);
+        const float sg = 1.f / (1.f + expf(-z));
+        float v = src[d] * rstd;
+        if (w) v *= w[d];
+        dst[d] = from_f32<T>(v * (gate_act ? z * sg : sg));
+    }
+}
+
+extern "C" int vx_head_norm_gate(const float* o, const void* g, int ldg, const float* w, void* out, int rows, int H,
+                                 int Dv, float eps, int gate_act, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return VX_OK;
+    if (H <= 0 || Dv <= 0 || ldg < H * Dv) return VX_ERR_SHAPE;
+    const int warps = 4;
+    const long long blocks = ((long long)rows * H + warps - 1) / warps;
+    if (blocks > 0x7fffffffLL) return VX_ERR_LIMIT;
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (head_norm_gate_kernel<float>), (unsigned)blocks, warps * 32, 0, stream, o, (const float*)g, ldg, w, (float*)out, rows, H, Dv, eps, gate_act);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (head_norm_gate_kernel<bf16>), (unsigned)blocks, warps * 32, 0, stream, o, (const bf16*)g, ldg, w, (bf16*)out, rows, H, Dv, eps, gate_act);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// One block per token.  down [tokens, ldd]: C latent channels, then R channels of the key part that all heads
+// share.  The latent part is RMS-normed with a plain weight and written, followed by the rotated key part
+// (pairs (2i, 2i + 1) when `interleaved`, else (i, i + R/2), angle position * inv_freq[i]), to
+// pool[slot] (rows of C + R elements; a negative slot writes nothing).  The queries q [tokens, ldq] hold, per
+// head, D channels that stay and then R that are rotated the same way and written to the last R channels of the
+// head's row of qa [tokens, H, C + R] (whose first C channels another kernel fills).
+template <typename T>
+__global__ void latent_prep_kernel(const T* __restrict__ down, int ldd, const T* __restrict__ q, int ldq, T* __restrict__ qa,
+                                   const float* __restrict__ w, float eps, const float* __restrict__ inv_freq,
+                                   int interleaved, const int* __restrict__ positions,
+                                   const int* __restrict__ slot_mapping, T* __restrict__ pool, int H, int D, int R, int C) {
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    const int half = R >> 1;
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    const T* dr = down + (size_t)t * ldd;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < C; i += blockDim.x) { const float v = to_f32(dr[i]); ss += v * v; }
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)C + eps);
+    if (slot >= 0) {
+        T* dst = pool + (size_t)slot * (C + R);
+        for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = from_f32<T>(to_f32(dr[i]) * rstd * w[i]);
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            float sn, cs;
+            sincosf(pos * inv_freq[i], &sn, &cs);
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            const float a = to_f32(dr[C + ia]), b = to_f32(dr[C + ib]);
+            dst[C + ia] = from_f32<T>(a * cs - b * sn);
+            dst[C + ib] = from_f32<T>(b * cs + a * sn);
+        }
+    }
+    for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+        const int h = i / half, p = i - h * half;
+        float sn, cs;
+        sincosf(pos * inv_freq[p], &sn, &cs);
+        const T* qr = q + (size_t)t * ldq + (size_t)h * (D + R) + D;
+        T* qo = qa + ((size_t)t * H + h) * (C + R) + C;
+        const int ia = interleaved ? 2 * p : p, ib = interleaved ? 2 * p + 1 : p + half;
+        const float a = to_f32(qr[ia]), b = to_f32(qr[ib]);
+        qo[ia] = from_f32<T>(a * cs - b * sn);
+        qo[ib] = from_f32<T>(b * cs + a * sn);
+    }
+}
+
+extern "C" int vx_latent_prep(const void* down, int ldd, const void* q, int ldq, void* qa, const float* w, float eps,
+                              const float* inv_freq, int interleaved, const int* positions, const int* slot_mapping,
+                              void* pool, int tokens, int H, int D, int R, int C, int dtype, cudaStream_t stream) {
+    if (tokens <= 0) return VX_OK;
+    if (H <= 0 || D < 0 || R < 0 || (R & 1) || C <= 0 || ldd < C + R || ldq < H * (D + R)) return VX_ERR_SHAPE;
+    if (R > 0 && !inv_freq) return VX_ERR_SHAPE;
+    if (slot_mapping && !pool) return VX_ERR_SHAPE;
+    const int threads = C >= 512 ? 256 : 128;
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ROPE, (latent_prep_kernel<float>), tokens, threads, 0, stream, (const float*)down, ldd, (const float*)q, ldq, (float*)qa, w, eps, inv_freq, interleaved, positions, slot_mapping, (float*)pool, H, D, R, C);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ROPE, (latent_prep_kernel<bf16>), tokens, threads, 0, stream, (const bf16*)down, ldd, (const bf16*)q, ldq, (bf16*)qa, w, eps, inv_freq, interleaved, positions, slot_mapping, (bf16*)pool, H, D, R, C);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// sums [rows, 2 inner] float32: all gates, then all ups (without their biases); bias [2 inner] float32 or null.
+// g = min(gate, L), u = clamp(up, -L, L); out = g sigmoid(slope g) (u + 1) in T.
+template <typename T>
+__global__ void capped_gated_act_kernel(const float* __restrict__ sums, const float* __restrict__ bias, T* __restrict__ out,
+                                        long long total, int inner, float limit, float slope) {
+    pdl_wait();
+    pdl_trigger();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / inner;
+        const int c = (int)(i - r * inner);
+        float g = sums[r * 2 * inner + c], u = sums[r * 2 * inner + inner + c];
+        if (bias) { g += bias[c]; u += bias[inner + c]; }
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        out[i] = from_f32<T>(g / (1.f + expf(-slope * g)) * (u + 1.f));
+    }
+}
+
+extern "C" int vx_capped_gated_act(const float* sums, const float* bias, void* out, int rows, int inner, float limit,
+                                   float slope, int dtype, cudaStream_t stream) {
+    if (rows <= 0 || inner <= 0) return VX_OK;
+    const long long total = (long long)rows * inner;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (capped_gated_act_kernel<float>), blocks, 256, 0, stream, sums, bias, (float*)out, total, inner, limit, slope);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (capped_gated_act_kernel<bf16>), blocks, 256, 0, stream, sums, bias, (bf16*)out, total, inner, limit, slope);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// One block per row.  residual (float32, in place) += c0 y0 + c1 y1 + c2 y2 + rows_add + vec, every term
+// optional; then, with a weight, normed = residual / sqrt(mean(residual^2) + eps) * w in T.
+template <typename T>
+__global__ void sum_add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ y0, float c0,
+                                       const T* __restrict__ y1, float c1, const T* __restrict__ y2, float c2,
+                                       const float* __restrict__ rows_add, const float* __restrict__ vec,
+                                       const float* __restrict__ w, T* __restrict__ normed, int width, float eps) {
+    extern __shared__ float row_s[];
+    __shared__ float scratch[32];
+    pdl_wait();
+    pdl_trigger();
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = residual[base + i];
+        float add = 0.f;
+        if (y0) add = c0 * to_f32(y0[base + i]);
+        if (y1) add += c1 * to_f32(y1[base + i]);
+        if (y2) add += c2 * to_f32(y2[base + i]);
+        v += add;
+        if (rows_add) v += rows_add[base + i];
+        if (vec) v += vec[i];
+        residual[base + i] = v;
+        row_s[i] = v;
+        ss += v * v;
+    }
+    if (!w) return;
+    ss = block_sum(ss, scratch);
+    const float rstd = rsqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) normed[base + i] = from_f32<T>(row_s[i] * rstd * w[i]);
+}
+
+extern "C" int vx_sum_add_rmsnorm(float* residual, const void* y0, float c0, const void* y1, float c1, const void* y2,
+                                  float c2, const float* rows_add, const float* vec, const float* w, void* normed,
+                                  int rows, int width, float eps, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return VX_OK;
+    if (width <= 0 || (w && !normed)) return VX_ERR_SHAPE;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    const size_t smem = sizeof(float) * width;
+    if (smem > 48 * 1024) return VX_ERR_LIMIT;
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (sum_add_rmsnorm_kernel<float>), rows, threads, smem, stream, residual, (const float*)y0, c0, (const float*)y1, c1, (const float*)y2, c2, rows_add, vec, w, (float*)normed, width, eps);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (sum_add_rmsnorm_kernel<bf16>), rows, threads, smem, stream, residual, (const bf16*)y0, c0, (const bf16*)y1, c1, (const bf16*)y2, c2, rows_add, vec, w, (bf16*)normed, width, eps);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+__global__ void softcap_rows_kernel(const float* __restrict__ x, float* __restrict__ out, long long total, float cap) {
+    pdl_wait();
+    pdl_trigger();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x)
+        out[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int vx_softcap_rows(const float* x, float* out, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return VX_OK;
+    if (!(cap > 0.f)) return VX_ERR_SHAPE;
+    const int blocks = (int)((total + 255) / 256 > 148 * 16 ? 148 * 16 : (total + 255) / 256);
+    VX_LAUNCH_K(VX_K_ELEMENTWISE, softcap_rows_kernel, blocks, 256, 0, stream, x, out, total, cap);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}

@@ -9,8 +9,44 @@ from typing import Dict, List, Optional
 import torch
 
 from ..parts.base import Part, Runtime, TensorSpec
+from ..parts.block import PendingSum
 from ..parts.plan import ModelPlan
 from ..parts.registry import build_part, part_class
+
+
+class StreamInputs(Part):
+    """What a plan adds to the stream between layers (`ModelPlan.stream_inputs`): holds the tensors of vectors
+    (float32) and says, per place, what is to be added."""
+    cuda_graph_safe = True
+
+    def __init__(self, inputs, hidden_size: int):
+        super().__init__("")
+        self.hidden_size = int(hidden_size)
+        self.by_place = {x.place: x for x in inputs}
+        self.shapes = {}
+        for x in inputs:
+            if x.tensor is not None:
+                if self.shapes.setdefault(x.tensor, x.rows) != x.rows:
+                    raise ValueError("stream inputs disagree about the rows of %r" % x.tensor)
+        self.vectors = {}
+
+    @property
+    def needs_embedding(self) -> bool:
+        return any(x.embedding for x in self.by_place.values())
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        return [TensorSpec(name, (rows, self.hidden_size), "bias") for name, rows in self.shapes.items()]
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(tensors, runtime)
+        self.vectors = {name: tensors[name].to(torch.float32).contiguous() for name in self.shapes}
+
+    def at(self, place: int, embedded):
+        """(float32 rows or None, float32 vector or None) that the stream takes before `place`."""
+        x = self.by_place.get(place)
+        if x is None:
+            return None, None
+        return (embedded if x.embedding else None), (self.vectors[x.tensor][x.row] if x.tensor is not None else None)
 
 
 class DecoderModel:
@@ -28,6 +64,9 @@ class DecoderModel:
         self.final_norm = build_part("norm", plan.final_norm)
         self.head = build_part("head", plan.head)
         self.order = plan.running_order()
+        self.stream_inputs = StreamInputs(plan.stream_inputs, plan.hidden_size) if plan.stream_inputs else None
+        # called as probe(place, stream [tokens, hidden] float32) after every place of the running order (tests, tools)
+        self.probe = None
         self.runtime: Optional[Runtime] = None
 
     # -- weights -------------------------------------------------------------
@@ -36,6 +75,8 @@ class DecoderModel:
         for b in self.blocks:
             out.extend(b.parts())
         out.extend([self.final_norm, self.head])
+        if self.stream_inputs is not None:
+            out.append(self.stream_inputs)
         return out
 
     def tensor_specs(self) -> List[TensorSpec]:
@@ -94,13 +135,37 @@ class DecoderModel:
         else:
             residual = self.embedding.forward(ctx)
         delta = None
+        inputs = self.stream_inputs
+        embedded = residual.clone() if inputs is not None and inputs.needs_embedding else None
         for place, i in enumerate(self.order):
-            residual, delta = self.blocks[i].forward(residual, delta, ctx, cache.layer(place))
-            if not getattr(self.blocks[i], "leaves_rounded", False):
+            block = self.blocks[i]
+            if inputs is not None:
+                rows, vector = inputs.at(place, embedded)
+                if rows is not None or vector is not None:
+                    # added with whatever the last block left to be added, by the kernel that norms the stream next
+                    if not isinstance(delta, PendingSum):
+                        delta = PendingSum([(delta, 1.0)] if delta is not None else [])
+                    delta.rows, delta.vector = rows, vector
+                    ctx.rounded = None
+            if isinstance(delta, PendingSum) and not getattr(block, "takes_pending", False):
+                delta.add_to(residual)
+                delta = None
+            residual, delta = block.forward(residual, delta, ctx, cache.layer(place))
+            if not getattr(block, "leaves_rounded", False):
                 ctx.rounded = None   # (a rounded copy of the stream is good for the block right after its maker)
+            if self.probe is not None:
+                done = residual.clone()
+                if isinstance(delta, PendingSum):
+                    delta.add_to(done)
+                elif delta is not None:
+                    done += delta
+                self.probe(place, done)
         return residual, delta
 
     def logits(self, residual, delta, rows: torch.Tensor) -> torch.Tensor:
         """float32 logits [len(rows), vocab] at the given token rows (int32)."""
+        if isinstance(delta, PendingSum):
+            delta.add_to(residual)
+            delta = None
         h = self.final_norm.add_norm(residual, delta, rows=rows)
         return self.head.forward(h)

@@ -1,11 +1,12 @@
 from .attention import PagedAttention
-from .base import (Block, CacheParts, Embedding, FeedForward, FixedState, Mixer, Norm, PagedKV, Part, Position, Runtime,
+from .base import (Block, CacheParts, Embedding, FeedForward, FixedState, Mixer, Norm, PagedKV, PagedLatent, Part, Position, Runtime,
                    TensorSpec)
-from .block import PostNormBlock, PreNormBlock, SandwichNormBlock
+from .block import ParallelSublayersBlock, PendingSum, PostNormBlock, PreNormBlock, SandwichNormBlock
 from .embedding import OutputHead, PairHashEmbedding, TokenEmbedding
 from .linear import Linear, matmul
-from .linear_attention import DecayedLinearAttention
-from .mlp import DenseMLP, GatedMLP
+from .latent_attention import LatentAttention
+from .linear_attention import DecayedLinearAttention, GatedLinearAttention
+from .mlp import CappedGatedMLP, DenseMLP, GatedMLP
 from .moe import RoutedExperts
 from .norm import RMSNorm
 from .parallel import ParallelMixer
@@ -16,9 +17,12 @@ from .registry import (build_part, part_class, register_block, register_feed_for
 
 register_part("mixer", "paged_attention", PagedAttention)
 register_part("mixer", "decayed_linear_attention", DecayedLinearAttention)
+register_part("mixer", "gated_linear_attention", GatedLinearAttention)
+register_part("mixer", "latent_attention", LatentAttention)
 register_part("mixer", "parallel", ParallelMixer)
 register_part("feed_forward", "gated_mlp", GatedMLP)
 register_part("feed_forward", "dense_mlp", DenseMLP)
+register_part("feed_forward", "capped_gated_mlp", CappedGatedMLP)
 register_part("feed_forward", "routed_experts", RoutedExperts)
 register_part("norm", "rms_norm", RMSNorm)
 register_part("position", "rotary", RotaryPosition)
@@ -26,6 +30,7 @@ register_part("position", "none", NoPosition)
 register_part("block", "pre_norm", PreNormBlock)
 register_part("block", "sandwich_norm", SandwichNormBlock)
 register_part("block", "post_norm", PostNormBlock)
+register_part("block", "parallel_sublayers", ParallelSublayersBlock)
 register_part("embedding", "token_embedding", TokenEmbedding)
 register_part("embedding", "pair_hash_embedding", PairHashEmbedding)
 register_part("head", "linear_head", OutputHead)

@@ -31,6 +31,10 @@ exp(sink_h), an entry without key or value that is not scaled, so a row's weight
 sigmoid(W_g x)_h before the output projection; W_g reads the mixer's input and rides as further rows of the
 fused projection matrix ([Wq; Wk; Wv; Wg], zero rows up to a multiple of 8), and the attention kernels apply
 the gate as they write a head's output.
+
+And two for designs that bound their scores and rotate neighbours: `score_softcap` c > 0 (a scaled score s becomes
+c tanh(s / c) before the softmax) and a rotary position whose `layout` is "interleaved" (channel 2i paired with
+2i + 1; the q/k kernel takes the layout as a flag).
 """
 from __future__ import annotations
 
@@ -69,8 +73,11 @@ class PagedAttention(Mixer):
                  keep_first: int = 0, distance_bias_exponent: float = 0.0,
                  names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"),
                  norm_names: Sequence[str] = ("q_norm.weight", "k_norm.weight"), sink: bool = False,
-                 output_gate: bool = False, sink_name: str = "sink", gate_name: str = "g"):
+                 output_gate: bool = False, sink_name: str = "sink", gate_name: str = "g", score_softcap: float = 0.0):
         super().__init__(prefix)
+        self.softcap = float(score_softcap)
+        if self.softcap < 0:
+            raise ValueError("%sscore_softcap must not be negative" % prefix)
         self.names = dict(zip(("q_proj", "k_proj", "v_proj", "o_proj"), names))
         self.norm_names = (prefix + norm_names[0], prefix + norm_names[1])
         self.sink, self.output_gate = bool(sink), bool(output_gate)
@@ -110,7 +117,7 @@ class PagedAttention(Mixer):
     def extended(self) -> bool:
         """True if the layer uses what only the kernels for biased, unequal or kept-first attention know."""
         return (self.v_head_dim != self.head_dim or self.keep_first > 0 or self.bias_exponent > 0 or self.sink
-                or self.output_gate)
+                or self.output_gate or self.softcap > 0)
 
     @property
     def gate_col(self) -> int:
@@ -190,7 +197,8 @@ class PagedAttention(Mixer):
         if self.position is None or rotary is not None:
             inv_freq, rot = rotary if rotary is not None else (None, 0)
             ops.qk_norm_rope_kv(qkv, qw, kw, self.eps, inv_freq, rot, ctx.positions, slots,
-                                cache.k_pool, cache.v_pool, H, Hk, D, self.v_head_dim)
+                                cache.k_pool, cache.v_pool, H, Hk, D, self.v_head_dim,
+                                interleaved=bool(getattr(self.position, "interleaved", False)))
         else:
             # An encoding the fused kernel does not know: norm in place, let the
             # part encode q and k in place, then write the cache.
@@ -212,13 +220,13 @@ class PagedAttention(Mixer):
         more = dict(sinks=self.sinks, gate_col=self.gate_col)
         page = cache.k_pool.shape[2]
         if (not ctx.decode_only and ctx.max_new >= TC_PREFILL_MIN_TOKENS and self.keep_first == 0 and self.bias_exponent == 0
-                and self.v_head_dim == D and ops.prefill_attention_tc_supported(qkv.dtype, D, page, H // Hk)):
+                and self.softcap == 0 and self.v_head_dim == D and ops.prefill_attention_tc_supported(qkv.dtype, D, page, H // Hk)):
             # prompt portions of heads of 128 without a bias by distance: the tcgen05 kernel, with the probabilities in two
             # bfloat16 halves (this path's softmax weights are 32-bit), the sink and the gate in its epilogue
             return ops.paged_prefill_attention_tc(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.cu_seqlens,
                                                   ctx.kv_offsets, self.scale, self.window, H, Hk, D, ctx.n_seqs, ctx.max_new,
                                                   qkv.shape[0], max_kv=ctx.max_kv, halves=True, **more)
-        if ops.biased_attention_supported(qkv.dtype, D, self.v_head_dim, cache.k_pool.shape[2]):
+        if self.softcap == 0 and ops.biased_attention_supported(qkv.dtype, D, self.v_head_dim, cache.k_pool.shape[2]):
             # a step of single tokens: every row with its own position, its keys dealt to the warps of a block
             if ctx.decode_only:
                 return ops.biased_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
@@ -232,7 +240,7 @@ class PagedAttention(Mixer):
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                            qkv.shape[0], v_head_dim=self.v_head_dim, keep_first=self.keep_first,
-                                           bias_exponent=self.bias_exponent, **more)
+                                           bias_exponent=self.bias_exponent, softcap=self.softcap, **more)
 
     def _attend(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim

@@ -38,7 +38,8 @@ class TensorSpec:
       norm:          1 + N(0, 0.05); held in float32 (an exact widening)
       bias:          N(0, 0.02); held in float32
       matrix_f32:    N(0, 0.02); held in float32 whatever the engine's element type (a router)
-      int_table:     integers; held as int32"""
+      int_table:     integers; held as int32
+    A dimension of -1 is left open: the file's tensor decides it, and the part reads it off when it binds."""
     name: str
     shape: Tuple[int, ...]
     role: str = "matrix"
@@ -65,6 +66,14 @@ class PagedKV:
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+
+@dataclass(frozen=True)
+class PagedLatent:
+    """One row of `width` elements per position in pages: what a latent attention keeps (the normed latent vector
+    followed by the rotated key part that its heads share).  Keys and values are raised from it, so nothing is
+    stored per head."""
+    width: int
 
 
 @dataclass(frozen=True)

@@ -21,11 +21,41 @@ block returns, so it hands on no delta.
 rounded to the engine's element type; the kernel that norms a sublayer's output and updates the residual
 also writes that rounding for the next sublayer, and the last one of a block leaves it in `ctx.rounded` for
 the next block.
+
+`ParallelSublayersBlock`: ONE norm, whose output both sublayers read:
+    h = norm(x);  x = x + mixer(h) + feed_forward(h)
+(the last term falls away in a layer without a feed-forward).  The sublayers' outputs are not added at once: they
+travel as a `PendingSum` to whoever norms the stream next (the next block of this kind, or the model before another
+block or the final norm), whose one kernel adds them to the float32 residual, with their coefficients, and norms the
+sum.  A mixer made of members side by side hands its members over unmerged with their coefficients
+(`forward_terms`), so their weighted sum is formed in float32 in that same kernel.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass, field
+from typing import List, Optional, Tuple
+
+import torch
+
 from ..csrc import ops
 from .base import Block
+
+
+@dataclass
+class PendingSum:
+    """What is still to be added to the float32 residual: up to three (tensor, coefficient) terms in the engine's
+    element type, float32 rows of the residual's shape, and a float32 vector added to every row."""
+    terms: List[Tuple[torch.Tensor, float]] = field(default_factory=list)
+    rows: Optional[torch.Tensor] = None
+    vector: Optional[torch.Tensor] = None
+
+    def add_to(self, residual: torch.Tensor, weight=None, eps: float = 0.0, out_dtype=None):
+        """Adds everything to `residual` in place; with a weight returns the RMS norm of the sum."""
+        terms = list(self.terms)
+        while len(terms) > 3:   # (more terms than the kernel takes: the first ones go ahead)
+            ops.sum_add_rmsnorm(residual, terms[:3])
+            terms = terms[3:]
+        return ops.sum_add_rmsnorm(residual, terms, self.rows, self.vector, weight, eps, out_dtype)
 
 
 class PreNormBlock(Block):
@@ -97,3 +127,31 @@ class SandwichNormBlock(Block):
             f = self.feed_forward.forward(h, ctx)
             ops.merge_norm_add_norm(residual, f, n["feed_forward_out"].weight, m, n["feed_forward_out"].eps)
         return residual, None
+
+
+class ParallelSublayersBlock(Block):
+    norm_names = ("shared",)
+    needs_feed_forward = False
+    takes_pending = True
+
+    def __init__(self, mixer, feed_forward, norms):
+        super().__init__(mixer, feed_forward, norms)
+        n = self.norms["shared"]
+        if not hasattr(n, "weight") or not hasattr(n, "eps"):
+            raise ValueError("ParallelSublayersBlock fuses its norm into the residual update and takes an RMS norm; got %s"
+                             % type(n).__name__)
+
+    def forward(self, residual, delta, ctx, cache):
+        n = self.norms["shared"]
+        dtype = self.mixer.runtime.dtype
+        if isinstance(delta, PendingSum):
+            h = delta.add_to(residual, n.weight, n.eps, dtype)
+        else:
+            h = n.add_norm(residual, delta)
+        if hasattr(self.mixer, "forward_terms"):
+            terms = list(self.mixer.forward_terms(h, ctx, cache))
+        else:
+            terms = [(self.mixer.forward(h, ctx, cache), 1.0)]
+        if self.feed_forward is not None:
+            terms.append((self.feed_forward.forward(h, ctx), 1.0))
+        return residual, PendingSum(terms)

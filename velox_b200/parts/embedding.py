@@ -6,7 +6,7 @@ tied (src/paged/qwen3.rs:966-976).  The embedding feeds the float32 residual
 stream; logits are always float32 (the reference leaves them in the model's
 element type, src/paged/qwen3.rs:1015).  Two multipliers for designs that have them:
 `TokenEmbedding(scale=)` on the rows that enter the stream, `OutputHead(logit_scale=)`
-on the float32 logits.
+on the float32 logits; and a bound, `OutputHead(logit_softcap=c)`: logits become c tanh(logits / c).
 """
 from __future__ import annotations
 
@@ -87,8 +87,9 @@ class OutputHead(Part):
     cuda_graph_safe = True  # reads nothing of a step but device tensors and sizes fixed per graph
 
     def __init__(self, prefix: str, vocab_size: int, hidden_size: int, tied: bool = False, weight_name: str = "weight",
-                 logit_scale: float = 1.0):
+                 logit_scale: float = 1.0, logit_softcap: float = 0.0):
         super().__init__(prefix)
+        self.logit_softcap = float(logit_softcap)
         self.vocab_size, self.hidden_size, self.tied = int(vocab_size), int(hidden_size), bool(tied)
         self.logit_scale = float(logit_scale)
         self.weight_name = prefix + weight_name
@@ -113,4 +114,6 @@ class OutputHead(Part):
 
     def forward(self, rows: torch.Tensor) -> torch.Tensor:
         logits = matmul(rows, self.weight, None, torch.float32)
-        return logits if self.logit_scale == 1.0 else ops.scale_rows(logits, self.logit_scale)
+        if self.logit_scale != 1.0:
+            logits = ops.scale_rows(logits, self.logit_scale)
+        return ops.softcap_rows(logits, self.logit_softcap) if self.logit_softcap > 0 else logits

@@ -102,3 +102,43 @@ class DenseMLP(FeedForward):
     def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
         u = self.up(h, torch.float32)
         return self.down(ops.act(u, self.activation, out_dtype=h.dtype))
+
+
+class CappedGatedMLP(FeedForward):
+    """down(g sigmoid(slope g) (u + 1)) with g = min(gate(x), limit) and u = clamp(up(x), -limit, limit); the three
+    projections may carry biases.  Gate and up are one matrix ([W_gate; W_up]); their float32 sums get the biases,
+    the bounds and the activation in one kernel and are rounded once."""
+    cuda_graph_safe = True
+
+    def __init__(self, prefix: str, hidden_size: int, intermediate_size: int, limit: float, slope: float = 1.702,
+                 bias: bool = True, names: Sequence[str] = ("gate", "up", "down"), bias_suffix: str = ".b"):
+        super().__init__(prefix)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.limit, self.slope, self.bias = float(limit), float(slope), bool(bias)
+        if not self.limit > 0:
+            raise ValueError("%slimit must be positive, got %r" % (prefix, limit))
+        self.names = tuple(prefix + n for n in names)   # gate, up, down
+        self.bias_names = tuple(n + bias_suffix for n in self.names)
+        self.gate_up: Optional[Linear] = None
+        self.down: Optional[Linear] = None
+        self.gate_up_bias = None
+
+    def tensor_specs(self) -> List[TensorSpec]:
+        e, i = self.hidden_size, self.intermediate_size
+        specs = [TensorSpec(self.names[0], (i, e), "matrix"), TensorSpec(self.names[1], (i, e), "matrix"),
+                 TensorSpec(self.names[2], (e, i), "matrix")]
+        if self.bias:
+            specs += [TensorSpec(self.bias_names[0], (i,), "bias"), TensorSpec(self.bias_names[1], (i,), "bias"),
+                      TensorSpec(self.bias_names[2], (e,), "bias")]
+        return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
+        super().bind(tensors, runtime)
+        self.gate_up = Linear(torch.cat([tensors[self.names[0]], tensors[self.names[1]]], 0).contiguous())
+        if self.bias:
+            self.gate_up_bias = torch.cat([tensors[self.bias_names[0]], tensors[self.bias_names[1]]]).contiguous()
+        self.down = Linear(tensors[self.names[2]], tensors[self.bias_names[2]] if self.bias else None)
+
+    def forward(self, h: torch.Tensor, ctx=None) -> torch.Tensor:
+        sums = self.gate_up(h, torch.float32)
+        return self.down(ops.capped_gated_act(sums, self.gate_up_bias, self.limit, self.slope, h.dtype))

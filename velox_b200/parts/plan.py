@@ -8,7 +8,8 @@ can have different mixers and feed-forwards in different layers.  `order` is the
 list of layer indices in running order; it may name a layer twice: the two runs
 share the layer's weights, and each has a cache of its own.  A layer with
 `cache_of = j` keeps no cache and reads (and does not write) the cache that the
-latest earlier run of layer j filled.
+latest earlier run of layer j filled.  `stream_inputs` names what is added to the stream right before a place of
+the running order: the embedding's output once more, and/or a row of a tensor of vectors.
 """
 from __future__ import annotations
 
@@ -40,6 +41,17 @@ class LayerSpec:
 
 
 @dataclass(frozen=True)
+class StreamInput:
+    """Before place `place` of the running order the stream takes, in float32: the embedding's output as it entered
+    the first layer (`embedding`), and row `row` of the tensor `tensor` [`rows`, hidden] (None: no vector)."""
+    place: int
+    embedding: bool = False
+    tensor: Optional[str] = None
+    row: int = 0
+    rows: int = 1
+
+
+@dataclass(frozen=True)
 class ModelPlan:
     vocab_size: int
     hidden_size: int
@@ -51,6 +63,7 @@ class ModelPlan:
     max_positions: int = 0
     # names that a checkpoint may hold and the model does not use (no error to find them)
     ignored_tensors: List[str] = field(default_factory=list)
+    stream_inputs: List[StreamInput] = field(default_factory=list)
 
     def running_order(self) -> List[int]:
         return list(self.order) if self.order else list(range(len(self.layers)))
@@ -60,6 +73,13 @@ class ModelPlan:
         for i in self.running_order():
             if not 0 <= i < n:
                 raise ValueError("order names layer %d but the plan has %d layers" % (i, n))
+        seen = set()
+        for x in self.stream_inputs:
+            if not 0 <= x.place < len(self.running_order()) or x.place in seen:
+                raise ValueError("stream input at place %r: not a place of the running order, or named twice" % (x.place,))
+            if x.tensor is not None and not 0 <= x.row < x.rows:
+                raise ValueError("stream input at place %d takes row %d of %d" % (x.place, x.row, x.rows))
+            seen.add(x.place)
         for i, layer in enumerate(self.layers):
             j = layer.cache_of
             if j is None:

@@ -8,6 +8,9 @@ float64 and the quotient in float32 as the reference does
 and rounds the table to the model's element type (src/paged/qwen3.rs:287-293);
 here angle, sine and cosine are float32 inside the kernel and never rounded.
 
+With `layout="interleaved"` the same angles turn neighbours instead: channel 2i is paired with channel 2i + 1.
+The kernels that rotate take the layout as a flag (`interleaved`).
+
 `NoPosition`: nothing is applied.
 """
 from __future__ import annotations
@@ -23,8 +26,12 @@ from .base import Position
 class RotaryPosition(Position):
     cuda_graph_safe = True
 
-    def __init__(self, prefix: str = "", head_dim: int = 0, theta: float = 10000.0, rotary_dim: Optional[int] = None):
+    def __init__(self, prefix: str = "", head_dim: int = 0, theta: float = 10000.0, rotary_dim: Optional[int] = None,
+                 layout: str = "half"):
         super().__init__(prefix)
+        if layout not in ("half", "interleaved"):
+            raise ValueError("rotation layout %r is not 'half' or 'interleaved'" % (layout,))
+        self.interleaved = layout == "interleaved"
         self.head_dim = int(head_dim)
         self.theta = float(theta)
         self.rotary_dim = int(rotary_dim) if rotary_dim else self.head_dim

@@ -90,7 +90,8 @@ def load_weights(model, folder: str, runtime: Runtime) -> None:
         if s.name not in where:
             continue
         dt, shape = where[s.name].info(s.name)
-        if tuple(shape) != tuple(s.shape):
+        # (a dimension that a part leaves open, -1, is whatever the file holds; the part checks it when it binds)
+        if len(shape) != len(s.shape) or any(w != -1 and w != g for w, g in zip(s.shape, shape)):
             wrong_shape.append((s.name, s.shape, shape))
         ok = dt in _INTS if s.role == "int_table" else dt in _FLOATS
         if not ok:

@@ -35,6 +35,8 @@ def _generator(seed: int, name: str, device="cpu") -> torch.Generator:
 
 def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu") -> torch.Tensor:
     g = _generator(seed, spec.name, device)
+    if any(d < 0 for d in spec.shape):
+        raise ValueError("tensor %r has a dimension that only a file gives; random weights need it in the configuration" % spec.name)
     if spec.role == "int_table":
         return torch.randint(0, 1 << 15, spec.shape, generator=g, dtype=torch.int32, device=device)
     x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
