@@ -569,6 +569,156 @@ def buvuzen_kernels(pk, sz):
     return rows
 
 
+# ---- Kapuvik beside Dobepel at equal size (`--workload kapuvik`) ----------------------------------------
+# The same widths and head counts as above, four layers: latent attention (heads of 128 + 64 rotated channels, values of
+# 128, a latent row of 512), two layers of linear attention with a decay per channel (128 x 128 state a head, a decay
+# projection through 16 channels), and one with softmax attention (heads of 128, scores bounded at 30) beside rotated
+# linear attention with a fixed decay.  The dense feed-forward has the size that a Dobepel token runs through.  Dobepel is
+# the closest existing model: the same side-by-side mixer of softmax attention and fixed-decay linear attention.
+KAPUVIK_RANK, KAPUVIK_ROT, KAPUVIK_DECAY_RANK, KAPUVIK_CAP = 512, 64, 16, 30.0
+
+
+def kapuvik_raw(sz):
+    ff = {"kind": "dense", "ff": DOBEPEL_TOP * sz["expert_ff"] + sz["shared_ff"], "limit": 7.0}
+    H, HL = sz["heads"], sz["lin_heads"]
+    latent = {"type": "latent_attention", "mlp": ff, "mixer": {
+        "heads": H, "dim": 128, "rot_dim": KAPUVIK_ROT, "vdim": 128, "kv_rank": KAPUVIK_RANK, "scale": 192 ** -0.5,
+        "rot": {"base": 10000.0, "dims": KAPUVIK_ROT}}}
+    gla = {"type": "gla", "mlp": ff, "mixer": {"heads": HL, "dim": 128, "vdim": 128, "tau": 16.0, "rank": KAPUVIK_DECAY_RANK}}
+    left = {"heads": H, "kv_heads": sz["kv_heads"], "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": KAPUVIK_CAP,
+            "rot": {"base": 10000.0, "dims": 128}}
+    right = {"heads": HL, "dim": 128, "vdim": 128, "rot": {"base": 10000.0, "dims": 64},
+             "decay": [1.0 - 2.0 ** (-5.0 - 5.0 * h / max(1, HL - 1)) for h in range(HL)]}
+    both = {"type": "parallel", "mlp": ff, "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.9}}
+    return {"architecture": "Kapuvik", "vocab": DOBEPEL_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 0.5}, "logit_softcap": 15.0,
+            "layers": [json.loads(json.dumps(x)) for x in (latent, gla, gla, both)]}
+
+
+def kapuvik_workload(args, pk):
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at 2,048 cached tokens) of Kapuvik and of
+    Dobepel at equal width and depth, through the step function, timed with CUDA events; then the design's own kernels
+    beside Dobepel's like kernels at the 2k size, each as a fraction of its roofline."""
+    import torch
+    from velox_b200.config import DobepelConfig, KapuvikConfig
+
+    T, B, CTX = 2048, 8, 2048
+    K, W = max(1, min(args.steps, 32)), max(3, args.warmup)
+    gen = torch.Generator().manual_seed(SEED)
+    sizes = {}
+    four = lambda sz: dict(sz, layers=4)
+    model_points(KapuvikConfig.from_dict(kapuvik_raw(four(DOBEPEL_SIZES["1k"]))), DOBEPEL_VOCAB, T, B, CTX, K, W, gen)  # thrown away
+    for name, sz in DOBEPEL_SIZES.items():
+        sz = four(sz)
+        sizes[name] = {"kapuvik": model_points(KapuvikConfig.from_dict(kapuvik_raw(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "dobepel": model_points(DobepelConfig.from_dict(dobepel_raw(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "shape": sz}
+    return {"metric": "Kapuvik beside Dobepel at equal size: prefill of %d tokens, decode at batch %d with %d cached tokens, bf16"
+                      % (T, B, CTX), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "sizes": sizes,
+            "value": sizes["2k"]["kapuvik"]["decode_tok_s"], "higher_is_better": True,
+            "kernels": kapuvik_kernels(pk, four(DOBEPEL_SIZES["2k"])), "peaks": pk,
+            "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids"}
+
+
+def kapuvik_kernels(pk, sz):
+    """Microseconds and fractions of the roofline of Kapuvik's kernels beside Dobepel's like kernels at one size."""
+    import torch
+    from velox_b200.csrc import ops
+    dev, bf = "cuda:0", torch.bfloat16
+    E, H, G, HL, D = sz["width"], sz["heads"], sz["kv_heads"], sz["lin_heads"], 128
+    C, R = KAPUVIK_RANK, KAPUVIK_ROT
+    T, B, CTX, S = 2048, 8, 2048, PAGE
+    rows, row, us = kernel_rows(pk)
+    ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    pages = B * (CTX // S)
+    kp = torch.randn((pages, G, S, D), device=dev).to(bf)
+    vp = torch.randn((pages, G, S, D), device=dev).to(bf)
+    bt = torch.arange(pages, dtype=torch.int32, device=dev).view(B, CTX // S)
+    cu, off = ints([0, T]), ints([0])
+    seq_t, pos_t = ints([0] * T), ints(list(range(T)))
+    seqs, pos = ints(list(range(B))), ints([CTX - 1] * B)
+    # -- softmax attention with bounded scores: a prompt of T tokens, then B single tokens at CTX cached tokens --
+    q = torch.randn((T, (H + 2 * G) * D), device=dev).to(bf)
+    qd = torch.randn((B, (H + 2 * G) * D), device=dev).to(bf)
+    fl = 2.0 * (T * (T + 1) // 2) * 2 * D * H
+    nb = B * G * CTX * 2 * D * 2.0
+    if ops.biased_attention_supported(bf, D, D, S):
+        row("prompt attention, bounded scores (mma.sync, P in two halves)", us(lambda: ops.biased_prefill_attention(
+            q, q.shape[1], kp, vp, bt, cu, off, D ** -0.5, 0, 0, 0.0, H, G, D, D, 1, T, T, softcap=KAPUVIK_CAP)), fl)
+        row("prompt attention, Dobepel (biased, no window)", us(lambda: ops.biased_prefill_attention(
+            q, q.shape[1], kp, vp, bt, cu, off, D ** -0.5, 0, 0, 8.0, H, G, D, D, 1, T, T)), fl)
+        row("decode attention, bounded scores", us(lambda: ops.biased_decode_attention(
+            qd, qd.shape[1], kp, vp, bt, seqs, pos, D ** -0.5, 0, 0, 0.0, H, G, D, D, B, max_kv=CTX, softcap=KAPUVIK_CAP), 50), 0.0, nb)
+        row("decode attention, Dobepel (biased, no window)", us(lambda: ops.biased_decode_attention(
+            qd, qd.shape[1], kp, vp, bt, seqs, pos, D ** -0.5, 0, 0, 8.0, H, G, D, D, B, max_kv=CTX), 50), 0.0, nb)
+    # -- latent attention: rows of C + R elements, one key/value head for all query heads --
+    lp = torch.randn((pages, 1, S, C + R), device=dev).to(bf)
+    qa = torch.randn((T, H, C + R), device=dev).to(bf)
+    qad = torch.randn((B, H, C + R), device=dev).to(bf)
+    lfl = 2.0 * (T * (T + 1) // 2) * (2 * C + R) * H
+    lnb = B * CTX * (C + R) * 2.0
+    row("prompt latent attention (folded queries over cached rows)", us(lambda: ops.latent_attention(
+        qa, lp, bt, seq_t, pos_t, 192 ** -0.5, H, C, R, max_kv=T), 3), lfl)
+    row("decode latent attention", us(lambda: ops.latent_attention(
+        qad, lp, bt, seqs, pos, 192 ** -0.5, H, C, R, max_kv=CTX), 20), 0.0, lnb)
+    down, qq = torch.randn((T, C + R), device=dev).to(bf), torch.randn((T, H * (D + R)), device=dev).to(bf)
+    slots = torch.randperm(pages * S, device=dev)[:T].to(torch.int32)
+    inv64 = (1e4 ** (-torch.arange(0, R, 2, device=dev, dtype=torch.float32) / R)).contiguous()
+    wl = torch.ones(C, device=dev)
+    qa3 = qa
+    row("latent row: norm + rotation + cache write + query rotation, %d tokens" % T, us(lambda: ops.latent_prep(
+        down, qq, qa3, wl, 1e-6, inv64, True, pos_t, slots, lp, H, D, R, C)), 0.0, T * ((C + R) * 4 + H * R * 4.0))
+    inv128 = (1e4 ** (-torch.arange(0, D, 2, device=dev, dtype=torch.float32) / D)).contiguous()
+    row("Dobepel/Qwen3: q/k rotation + cache write, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
+        q, None, None, 1e-6, inv128, D, pos_t, slots, kp, vp, H, G, D, D)), 0.0, T * (H + 2 * G) * D * 2 * 2.0)
+    # -- linear attention --
+    x = (torch.randn((T, 4 * HL * D), device=dev) * 0.5).to(bf)
+    xd = (torch.randn((B, 4 * HL * D), device=dev) * 0.5).to(bf)
+    decay = torch.full((HL,), 0.97, device=dev)
+    state = torch.zeros((B, HL, D, D), device=dev)
+    gate, gated = torch.randn((T, HL * D), device=dev) + 2.0, torch.randn((B, HL * D), device=dev) + 2.0
+    slot0, cu_b, slots_b = ints([0]), ints(list(range(B + 1))), ints(list(range(B)))
+    lin_fl = T * HL * 2.0 * (32 * 2 * D + 2 * D * D)
+    sb = B * HL * D * D * 4 * 2.0
+    inv_r = (1e4 ** (-torch.arange(0, 64, 2, device=dev, dtype=torch.float32) / 64)).contiguous()
+    row("prompt linear attention, decay per channel (float32 operands)", us(lambda: ops.linear_attention_walk(
+        x, 0, HL * D, 2 * HL * D, state, cu, slot0, 1, HL, D, D, gate=gate, gate_mul=1 / 16.0, q_mul=D ** -0.5), 5), lin_fl)
+    row("prompt linear attention, rotated, fixed decay (float32 operands)", us(lambda: ops.linear_attention_walk(
+        x, 0, HL * D, 2 * HL * D, state, cu, slot0, 1, HL, D, D, decay=decay, inv_freq=inv_r, rot_dim=64, positions=pos_t,
+        k_mul=D ** -0.5), 5), lin_fl)
+    row("prompt linear attention, Dobepel (chunks side by side, mma.sync, halves)", us(lambda: ops.linear_attention(
+        x, 0, HL * D, 2 * HL * D, decay, state, cu, slot0, 1, T, HL, D, D)), lin_fl)
+    posd = ints([CTX - 1] * B)
+    row("decode linear attention, decay per channel", us(lambda: ops.linear_attention_walk(
+        xd, 0, HL * D, 2 * HL * D, state, cu_b, slots_b, B, HL, D, D, gate=gated, gate_mul=1 / 16.0, q_mul=D ** -0.5), 50), 0.0, sb)
+    row("decode linear attention, rotated, fixed decay", us(lambda: ops.linear_attention_walk(
+        xd, 0, HL * D, 2 * HL * D, state, cu_b, slots_b, B, HL, D, D, decay=decay, inv_freq=inv_r, rot_dim=64, positions=posd,
+        k_mul=D ** -0.5), 50), 0.0, sb)
+    row("decode linear attention, Dobepel (recurrent)", us(lambda: ops.linear_attention(
+        xd, 0, HL * D, 2 * HL * D, decay, state, cu_b, slots_b, B, 1, HL, D, D), 50), 0.0, sb)
+    big = 16384
+    o = torch.randn((big, HL * D), device=dev)
+    g = torch.randn((big, HL * D), device=dev).to(bf)
+    wv = torch.ones(D, device=dev)
+    row("per-head norm + silu gate, %d rows" % big, us(lambda: ops.head_norm_gate(o, g, wv, HL, 1e-6, "silu"), 10), 0.0, big * HL * D * 8.0)
+    wj = torch.ones(HL * D, device=dev)
+    row("Dobepel: joined norm + sigmoid gate, %d rows" % big, us(lambda: ops.gated_rmsnorm(o, g, wj, 1e-6), 10), 0.0, big * HL * D * 8.0)
+    # -- feed-forward activation, stream update --
+    I = DOBEPEL_TOP * sz["expert_ff"] + sz["shared_ff"]
+    sums = torch.randn((big, 2 * I), device=dev)
+    bias = torch.randn(2 * I, device=dev)
+    row("bounded gated activation on float32 sums + biases, %d rows" % big, us(lambda: ops.capped_gated_act(sums, bias, 7.0, 1.702, bf), 10),
+        0.0, big * I * (8 + 2.0))
+    res = torch.randn((big, E), device=dev)
+    y0, y1 = torch.randn((big, E), device=dev).to(bf), torch.randn((big, E), device=dev).to(bf)
+    w = torch.ones(E, device=dev)
+    row("stream += mixer + feed-forward, then the next norm, %d rows" % big,
+        us(lambda: ops.sum_add_rmsnorm(res, [(y0, 1.0), (y1, 1.0)], weight=w, eps=1e-6), 10), 0.0, big * E * (4 + 4 + 2 + 2 + 2.0))
+    row("Dobepel: two branch norms + sum + norm + residual + next norm, %d rows" % big,
+        us(lambda: ops.merge_norm_add_norm(res, y0, w, 0.5, 1e-6, w, 0.5, y1, w, 0.5, w_next=w), 10), 0.0, big * E * (4 + 4 + 2 + 2 + 2.0))
+    return rows
+
+
 def main() -> int:
     global CONTEXT, PROMPT
     ap = argparse.ArgumentParser()
@@ -578,12 +728,12 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=BATCH)
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "dobepel", "buvuzen"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "dobepel", "buvuzen", "kapuvik"],
                     help="decode: the benchmark (steady decoding at a fixed batch). stream: continuous batching "
                          "under arrivals (64 requests, prompts of 128-4,096 tokens, 256 new tokens each, Poisson "
                          "arrivals); prints its own JSON line. dobepel: the Dobepel design beside Qwen3 at equal size "
                          "(prefill, decode, and the design's kernels against their rooflines); its own JSON line. buvuzen: the same for "
-                         "the Buvuzen design beside Dobepel and Qwen3")
+                         "the Buvuzen design beside Dobepel and Qwen3. kapuvik: the same for the Kapuvik design beside Dobepel")
     ap.add_argument("--arrival-rate", type=float, default=16.0, help="stream: mean arrivals a second")
     ap.add_argument("--lazy-graphs", action="store_true",
                     help="stream: capture each decode graph when a step first needs it, inside the run")
@@ -614,9 +764,9 @@ def main() -> int:
     from velox_b200.csrc import ops
     from velox_b200.engine import StepEntry
 
-    if args.workload in ("dobepel", "buvuzen"):
+    if args.workload in ("dobepel", "buvuzen", "kapuvik"):
         with ClockSampler() as clocks:
-            res = (dobepel_workload if args.workload == "dobepel" else buvuzen_workload)(args, peaks())
+            res = {"dobepel": dobepel_workload, "buvuzen": buvuzen_workload, "kapuvik": kapuvik_workload}[args.workload](args, peaks())
         res["clocks"] = clocks.summary()
         print(json.dumps(res))
         return 0

@@ -3,10 +3,25 @@ package and knows no cache: every function takes all positions of one sequence a
 positions one by one).  `forward` takes the raw config.json dictionary and a dictionary of arrays by tensor name.
 
 Notation: x [T, E] the stream; h the normed input of a layer; matrices are stored [out, in] and applied as h W^T.
+`store` (the identity by default) is applied to whatever an engine with 16-bit activations would keep in them: the
+normed input, the outputs of matrix products, what feeds the next product.  With `store_bfloat16` a run shows what
+such rounding costs; norms, scores, softmax weights, decays, states and the stream stay exact in either run.
 """
 from __future__ import annotations
 
 import numpy as np
+
+
+def store_bfloat16(x):
+    """x rounded to bfloat16 (nearest even) and widened again."""
+    a = np.ascontiguousarray(x, dtype=np.float32)
+    bits = a.view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32).astype(np.float64).reshape(a.shape)
+
+
+def same(x):
+    return x
 
 
 def rms(x, eps):
@@ -64,19 +79,19 @@ def causal_softmax_attention(q, k, v, scale, softcap=0.0):
     return out
 
 
-def softmax_member(h, P, m, positions):
+def softmax_member(h, P, m, positions, store=same):
     """Grouped softmax attention with rotated q and k (pairs of neighbours), a score multiplier and a cap."""
     T = h.shape[0]
     H, G, D, Dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ P["q"].T).reshape(T, H, D)
-    k = (h @ P["k"].T).reshape(T, G, D)
-    v = (h @ P["v"].T).reshape(T, G, Dv)
+    q = store(h @ P["q"].T).reshape(T, H, D)
+    k = store(h @ P["k"].T).reshape(T, G, D)
+    v = store(h @ P["v"].T).reshape(T, G, Dv)
     rot = m.get("rot")
     if rot:
-        q = rotate(q, positions, rot["base"], rot["dims"], True)
-        k = rotate(k, positions, rot["base"], rot["dims"], True)
-    o = causal_softmax_attention(q, k, v, m["scale"], m.get("softcap") or 0.0)
-    return o.reshape(T, H * Dv) @ P["o"].T
+        q = store(rotate(q, positions, rot["base"], rot["dims"], True))
+        k = store(rotate(k, positions, rot["base"], rot["dims"], True))
+    o = store(causal_softmax_attention(q, k, v, m["scale"], m.get("softcap") or 0.0))
+    return store(o.reshape(T, H * Dv) @ P["o"].T)
 
 
 def decayed_state_walk(q, k, v, decay):
@@ -93,66 +108,66 @@ def decayed_state_walk(q, k, v, decay):
     return out
 
 
-def retention_member(h, P, m, positions, eps):
+def retention_member(h, P, m, positions, eps, store=same):
     """Linear attention with a fixed decay per head: rotated q and k (halves paired), k / sqrt(D), every head's output
     divided by its own root mean square, times silu of a gate projection."""
     T = h.shape[0]
     H, D, Dv = m["heads"], m["dim"], m["vdim"]
-    q = (h @ P["q"].T).reshape(T, H, D)
-    k = (h @ P["k"].T).reshape(T, H, D)
-    v = (h @ P["v"].T).reshape(T, H, Dv)
+    q = store(h @ P["q"].T).reshape(T, H, D)
+    k = store(h @ P["k"].T).reshape(T, H, D)
+    v = store(h @ P["v"].T).reshape(T, H, Dv)
     rot = m.get("rot")
     if rot:
         q = rotate(q, positions, rot["base"], rot["dims"], False)
         k = rotate(k, positions, rot["base"], rot["dims"], False)
     k = k * D ** -0.5
     o = rms(decayed_state_walk(q, k, v, np.asarray(m["decay"], dtype=np.float64)), eps)
-    return (o.reshape(T, H * Dv) * silu(h @ P["g"].T)) @ P["o"].T
+    return store(store(o.reshape(T, H * Dv) * silu(store(h @ P["g"].T))) @ P["o"].T)
 
 
-def side_by_side_mixer(h, P, m, positions, eps):
-    left = softmax_member(h, {n[5:]: t for n, t in P.items() if n.startswith("left.")}, m["left"], positions)
-    right = retention_member(h, {n[6:]: t for n, t in P.items() if n.startswith("right.")}, m["right"], positions, eps)
-    return m["left_scale"] * left + m["right_scale"] * right
+def side_by_side_mixer(h, P, m, positions, eps, store=same):
+    left = softmax_member(h, {n[5:]: t for n, t in P.items() if n.startswith("left.")}, m["left"], positions, store)
+    right = retention_member(h, {n[6:]: t for n, t in P.items() if n.startswith("right.")}, m["right"], positions, eps, store)
+    return m.get("left_scale", 1.0) * left + m.get("right_scale", 1.0) * right
 
 
-def latent_mixer(h, P, m, positions, eps):
+def latent_mixer(h, P, m, positions, eps, store=same):
     """Attention whose keys and values are raised from one normed latent vector per position; a rotated key part of its
     own is shared by all heads."""
     T = h.shape[0]
     H, D, R, Dv, C = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
-    q = (h @ P["q"].T).reshape(T, H, D + R)
-    down = h @ P["dkv"].T
-    c = rms(down[:, :C], eps) * P["dkv.norm"]
-    k_rot = rotate(down[:, None, C:], positions, m["rot"]["base"], R, True)           # [T, 1, R]
-    q_rot = rotate(q[:, :, D:], positions, m["rot"]["base"], R, True)
-    k_plain = (c @ P["uk"].T).reshape(T, H, D)
-    v = (c @ P["uv"].T).reshape(T, H, Dv)
+    q = store(h @ P["q"].T).reshape(T, H, D + R)
+    down = store(h @ P["dkv"].T)
+    c = store(rms(down[:, :C], eps) * P["dkv.norm"])
+    k_rot = store(rotate(down[:, None, C:], positions, m["rot"]["base"], R, True))           # [T, 1, R]
+    q_rot = store(rotate(q[:, :, D:], positions, m["rot"]["base"], R, True))
+    k_plain = store(c @ P["uk"].T).reshape(T, H, D)
+    v = store(c @ P["uv"].T).reshape(T, H, Dv)
     qq = np.concatenate([q[:, :, :D], q_rot], axis=2)
     kk = np.concatenate([k_plain, np.broadcast_to(k_rot, (T, H, R))], axis=2)
-    o = causal_softmax_attention(qq, kk, v, m["scale"])
-    return o.reshape(T, H * Dv) @ P["o"].T
+    o = store(causal_softmax_attention(qq, kk, v, m["scale"]))
+    return store(o.reshape(T, H * Dv) @ P["o"].T)
 
 
-def gated_decay_mixer(h, P, m, eps):
+def gated_decay_mixer(h, P, m, eps, store=same):
     """Linear attention whose decay is a number per key channel and position, from a two-step projection."""
     T = h.shape[0]
     H, D, Dv = m["heads"], m["dim"], m["vdim"]
-    q = (h @ P["q"].T).reshape(T, H, D) * D ** -0.5
-    k = (h @ P["k"].T).reshape(T, H, D)
-    v = (h @ P["v"].T).reshape(T, H, Dv)
-    z = (h @ P["a1"].T) @ P["a2"].T + P["a2.b"]
+    q = store(h @ P["q"].T).reshape(T, H, D) * D ** -0.5
+    k = store(h @ P["k"].T).reshape(T, H, D)
+    v = store(h @ P["v"].T).reshape(T, H, Dv)
+    z = store(h @ P["a1"].T) @ P["a2"].T + P["a2.b"]
     alpha = (sigmoid(z) ** (1.0 / m["tau"])).reshape(T, H, D)
     o = rms(decayed_state_walk(q, k, v, alpha), eps) * P["norm"]
-    return (o.reshape(T, H * Dv) * silu(h @ P["g"].T)) @ P["o"].T
+    return store(store(o.reshape(T, H * Dv) * silu(store(h @ P["g"].T))) @ P["o"].T)
 
 
-def capped_feed_forward(h, P, m):
+def capped_feed_forward(h, P, m, store=same):
     """g = min(gate, L); u = clamp(up, -L, L); down(g sigmoid(1.702 g) (u + 1)); every projection has a bias."""
     L = m["limit"]
     g = np.minimum(h @ P["gate"].T + P["gate.b"], L)
     u = np.clip(h @ P["up"].T + P["up.b"], -L, L)
-    return (g * sigmoid(1.702 * g) * (u + 1.0)) @ P["down"].T + P["down.b"]
+    return store(store(g * sigmoid(1.702 * g) * (u + 1.0)) @ P["down"].T + P["down.b"])
 
 
 def running_order(cfg):
@@ -168,13 +183,13 @@ def running_order(cfg):
     return out + [(i, None, False) for i in range(b, n)]
 
 
-def forward(cfg, W, tokens, return_layers=False):
+def forward(cfg, W, tokens, return_layers=False, store=same):
     """float64 logits [T, vocab] of one sequence (and the stream after every layer run)."""
     W = {n: np.asarray(t, dtype=np.float64) for n, t in W.items()}
     eps = cfg["norm"]["eps"]
     T = len(tokens)
     positions = np.arange(T)
-    x0 = W["embed"][np.asarray(tokens)] * cfg["embedding"]["scale"]
+    x0 = W["embed"][np.asarray(tokens)] * (cfg.get("embedding") or {}).get("scale", 1.0)
     x = x0.copy()
     seen = []
     for i, t, first in running_order(cfg):
@@ -184,24 +199,32 @@ def forward(cfg, W, tokens, return_layers=False):
             x = x + W["loop.step"][t]
         layer = cfg["layers"][i]
         p = "l%d." % i
-        h = offset_norm(x, W[p + "norm1"], eps)
+        h = store(offset_norm(x, W[p + "norm1"], eps))
         M = {n[len(p) + 4:]: a for n, a in W.items() if n.startswith(p + "mix.")}
         kind = layer["type"]
         if kind == "parallel":
-            y = side_by_side_mixer(h, M, layer["mixer"], positions, eps)
+            y = side_by_side_mixer(h, M, layer["mixer"], positions, eps, store)
         elif kind == "latent_attention":
-            y = latent_mixer(h, M, layer["mixer"], positions, eps)
+            y = latent_mixer(h, M, layer["mixer"], positions, eps, store)
         elif kind == "gla":
-            y = gated_decay_mixer(h, M, layer["mixer"], eps)
+            y = gated_decay_mixer(h, M, layer["mixer"], eps, store)
         else:
             raise ValueError(kind)
         if layer.get("mlp") is not None:
             F = {n[len(p) + 4:]: a for n, a in W.items() if n.startswith(p + "mlp.")}
-            y = y + capped_feed_forward(h, F, layer["mlp"])
+            y = y + capped_feed_forward(h, F, layer["mlp"], store)
         x = x + y
         seen.append(x.copy())
-    logits = offset_norm(x, W["final.norm"], eps) @ W["head"].T
+    logits = store(offset_norm(x, W["final.norm"], eps)) @ W["head"].T
     cap = cfg.get("logit_softcap") or 0.0
     if cap:
         logits = cap * np.tanh(logits / cap)
     return (logits, np.stack(seen)) if return_layers else logits
+
+
+def greedy_generate(cfg, W, prompt, new_tokens):
+    """The `new_tokens` most likely tokens one after the other (the lowest id among equals)."""
+    toks = list(prompt)
+    for _ in range(new_tokens):
+        toks.append(int(np.argmax(forward(cfg, W, toks)[-1])))
+    return toks[len(prompt):]

@@ -57,6 +57,12 @@ __device__ __forceinline__ float ab_gate(const bf16* q, int q_row_stride, int ro
     return 1.f / (1.f + __expf(-__bfloat162float(q[(size_t)row * q_row_stride + gate_col + head])));
 }
 
+// A raw dot product as a score in units of log2: times scale, or, with a bound c on the scores (cap_log2 = c log2(e),
+// cap_arg = scale / c), c tanh(dot * scale / c).
+__device__ __forceinline__ float ab_score(float dot, float scale_log2, float cap_log2, float cap_arg) {
+    return cap_arg > 0.f ? cap_log2 * tanhf(dot * cap_arg) : dot * scale_log2;
+}
+
 struct AbSegments {
     const int* cu_seqlens;    // portions: rows of segment s are [cu_seqlens[s], cu_seqlens[s + 1])
     const int* kv_offsets;    //           at positions kv_offsets[s] ..
@@ -70,7 +76,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                         const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
                         AbSegments seg, bf16* __restrict__ out, int out_row_stride, float scale_log2, float bias_exp,
                         int window, int keep_first, int H, int Hk, int S, int share_log2,
-                        const float* __restrict__ sinks, int gate_col) {
+                        const float* __restrict__ sinks, int gate_col, float cap_log2, float cap_arg) {
     extern __shared__ __align__(128) unsigned char ab_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
     constexpr int KCHP = ab_pow2(KCH), VCHP = ab_pow2(VCH);   // a row's place in shared memory: chunks up to a power of two
@@ -241,7 +247,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                             const int key = key_base + kg * 16 + nt * 8 + ((lane & 3) << 1) + c;
                             const bool ok = vis[kg] && key <= pos && (key >= lo || key < kept);
                             float& v = sc[kg][nt][2 * hrow + c];
-                            v = ok ? v * scale_log2 - sl * (float)(pos - key) : -INFINITY;
+                            v = ok ? ab_score(v, scale_log2, cap_log2, cap_arg) - sl * (float)(pos - key) : -INFINITY;
                             mx = fmaxf(mx, v);
                         }
                 mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -339,7 +345,8 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
                      const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
                      const int* __restrict__ seq_of_token, const int* __restrict__ positions, bf16* __restrict__ out,
                      int out_row_stride, float scale_log2, float bias_exp, int window, int keep_first, int H, int Hk,
-                     int S, int share_log2, float* __restrict__ scratch, const float* __restrict__ sinks, int gate_col) {
+                     int S, int share_log2, float* __restrict__ scratch, const float* __restrict__ sinks, int gate_col,
+                     float cap_log2, float cap_arg) {
     extern __shared__ __align__(128) unsigned char ad_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
     constexpr int KCHP = ab_pow2(KCH), VCHP = ab_pow2(VCH);
@@ -446,7 +453,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
                     const int n = g * 16 + nt * 8 + ((lane & 3) << 1) + c;
                     const int key = n < nkept ? n : start + n - nkept;
                     float& v = sc[nt][2 * hrow + c];
-                    v = n < nkeys ? v * scale_log2 - sl[hrow] * (float)(pos - key) : -INFINITY;
+                    v = n < nkeys ? ab_score(v, scale_log2, cap_log2, cap_arg) - sl[hrow] * (float)(pos - key) : -INFINITY;
                     mx = fmaxf(mx, v);
                 }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
@@ -563,7 +570,7 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
                                 const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
                                 bf16* out, int out_row_stride, float scale, float bias_exp, int window, int keep_first,
                                 int tokens, int H, int Hk, int S, float* scratch, int runs, const float* sinks, int gate_col,
-                                cudaStream_t stream) {
+                                float softcap, cudaStream_t stream) {
     constexpr int KROW = ab_pow2(DK / 8) * 16, VROW = ab_pow2(DV / 8) * 16;
     const size_t walk = (size_t)AD_WARPS * 2 * (16 * KROW + 16 * VROW), parts = (size_t)AD_WARPS * 16 * (DV + 2) * 4;
     const size_t smem = 16 * KROW + (walk > parts ? walk : parts);
@@ -577,7 +584,8 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
     dim3 grid(share_log2 ? Hk : H, tokens, runs);
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_decode_kernel<DK, DV>), grid, AD_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
                 v_pool, block_table, max_blocks, seq_of_token, positions, out, out_row_stride, scale * AB_LOG2E, bias_exp,
-                window, keep_first, H, Hk, S, share_log2, scratch, sinks, gate_col);
+                window, keep_first, H, Hk, S, share_log2, scratch, sinks, gate_col, softcap * AB_LOG2E,
+                softcap > 0.f ? scale / softcap : 0.f);
     if (runs > 1)
         VX_LAUNCH_K(VX_K_JOIN, biased_decode_join_kernel, dim3(tokens, H), DV >= 128 ? 128 : 64, 0, stream, (const float*)scratch,
                     out, out_row_stride, H, DV, runs, sinks, q, q_row_stride, gate_col);
@@ -589,7 +597,7 @@ template <int DK, int DV>
 static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
                          int max_blocks, AbSegments seg, bf16* out, int out_row_stride, float scale, float bias_exp,
                          int window, int keep_first, int segments, int max_new, int H, int Hk, int S, const float* sinks,
-                         int gate_col, cudaStream_t stream) {
+                         int gate_col, float softcap, cudaStream_t stream) {
     constexpr int KROW = ab_pow2(DK / 8) * 16, VROW = ab_pow2(DV / 8) * 16;
     const size_t smem = (size_t)AB_BM * KROW + 2 * ((size_t)AB_BN * KROW + (size_t)AB_BN * VROW);
     static bool configured[VX_MAX_DEVICES];
@@ -602,7 +610,7 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
     dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, share_log2 ? Hk : H, segments);
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_attention_kernel<DK, DV>), grid, AB_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
                 v_pool, block_table, max_blocks, seg, out, out_row_stride, scale * AB_LOG2E, bias_exp, window, keep_first, H,
-                Hk, S, share_log2, sinks, gate_col);
+                Hk, S, share_log2, sinks, gate_col, softcap * AB_LOG2E, softcap > 0.f ? scale / softcap : 0.f);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -610,13 +618,15 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
 // Portions: cu_seqlens and kv_offsets given, `segments` requests of up to `max_new` tokens.  Single tokens:
 // cu_seqlens null, seq_of_token and positions given, `segments` token rows (max_new = 1); with `runs` > 1 and a
 // float32 scratch of segments * H * runs * (DV + 2) elements a token's keys are cut into runs, a block each.
-extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
-                                   const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
-                                   const int* seq_of_token, const int* positions, void* out, int out_row_stride,
-                                   float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
-                                   int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
-                                   int gate_col, cudaStream_t stream) {
+// With softcap c > 0 a scaled score s becomes c tanh(s / c) before the bias by distance and the softmax.
+extern "C" int vx_biased_attention_cap(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
+                                       const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
+                                       const int* seq_of_token, const int* positions, void* out, int out_row_stride,
+                                       float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
+                                       int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
+                                       int gate_col, float softcap, cudaStream_t stream) {
     if (segments <= 0 || max_new <= 0) return VX_OK;
+    if (softcap < 0.f) return VX_ERR_SHAPE;
     if (H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
     if (cu_seqlens ? !kv_offsets : (!seq_of_token || !positions || max_new != 1)) return VX_ERR_SHAPE;
     if (H > 65535 || segments > 65535) return VX_ERR_LIMIT;
@@ -628,7 +638,7 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
         return launch_biased_decode<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,       \
                                             block_table, max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, \
                                             scale, bias_exp, window, keep_first, segments, H, Hk, S, scratch, runs, sinks,  \
-                                            gate_col, stream)
+                                            gate_col, softcap, stream)
         AD_GO(64, 32); AD_GO(64, 64); AD_GO(64, 128); AD_GO(128, 32); AD_GO(128, 64); AD_GO(128, 128);
         AD_GO(32, 32); AD_GO(48, 48); AD_GO(80, 80); AD_GO(96, 96); AD_GO(112, 112);
 #undef AD_GO
@@ -639,9 +649,20 @@ extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* 
     if (DK == K_ && DV == V_)                                                                                             \
         return launch_biased<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, \
                                      max_blocks, seg, (bf16*)out, out_row_stride, scale, bias_exp, window, keep_first,    \
-                                     segments, max_new, H, Hk, S, sinks, gate_col, stream)
+                                     segments, max_new, H, Hk, S, sinks, gate_col, softcap, stream)
     AB_GO(64, 32); AB_GO(64, 64); AB_GO(64, 128); AB_GO(128, 32); AB_GO(128, 64); AB_GO(128, 128);
     AB_GO(32, 32); AB_GO(48, 48); AB_GO(80, 80); AB_GO(96, 96); AB_GO(112, 112);
 #undef AB_GO
     return VX_ERR_SHAPE;
+}
+
+extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
+                                   const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
+                                   const int* seq_of_token, const int* positions, void* out, int out_row_stride,
+                                   float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
+                                   int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
+                                   int gate_col, cudaStream_t stream) {
+    return vx_biased_attention_cap(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, cu_seqlens, kv_offsets,
+                                   seq_of_token, positions, out, out_row_stride, scale, bias_exp, window, keep_first, segments,
+                                   max_new, H, Hk, DK, DV, S, scratch, runs, sinks, gate_col, 0.f, stream);
 }

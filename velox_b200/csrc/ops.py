@@ -73,6 +73,8 @@ def _declare(lib) -> None:
         "vx_qk_norm_rope_kv": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, P],
         "vx_paged_attention_generic": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P, I, P],
         "vx_biased_attention": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P, I, P, I, P],
+        "vx_latent_attention": [P, P, P, I, P, P, P, P, F, I, I, I, I, I, I, I, P],
+        "vx_biased_attention_cap": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P, I, P, I, F, P],
         "vx_embedding_pair": [P, P, P, P, P, P, P, P, P, I, I, I, I, c_longlong, c_longlong, I, P],
         "vx_merge_norm_add_norm": [P, P, P, F, P, P, F, P, F, P, P, I, I, F, I, P],
         "vx_act": [P, I, P, I, I, I, I, I, P],
@@ -343,7 +345,7 @@ def biased_attention_supported(dtype, head_dim: int, v_head_dim: int, page_size:
 
 def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions,
                       scale, window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, segments,
-                      max_new, tokens, out, max_kv=0, sinks=None, gate_col=-1):
+                      max_new, tokens, out, max_kv=0, sinks=None, gate_col=-1, softcap=0.0):
     _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions, out, sinks)
     _check_sinks_gate("biased_attention", sinks, gate_col, num_heads, q_row_stride)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
@@ -361,37 +363,38 @@ def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, 
         runs = max(1, min(BIASED_DECODE_MAX_RUNS, -(-keys // 16) // 16))
         if runs > 1:
             scratch = workspace(q.device, tokens * num_heads * runs * (v_head_dim + 2), which="biased_decode")
-    _check(library().vx_biased_attention(
+    _check(library().vx_biased_attention_cap(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens),
         _ptr(kv_offsets), _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale),
         float(bias_exponent), int(window), int(keep_first), int(segments), int(max_new), num_heads, num_kv_heads, head_dim,
-        v_head_dim, k_pool.shape[2], _ptr(scratch), runs, _ptr(sinks), int(gate_col), _stream()), "biased_attention")
+        v_head_dim, k_pool.shape[2], _ptr(scratch), runs, _ptr(sinks), int(gate_col), float(softcap), _stream()),
+        "biased_attention")
     return out
 
 
 def biased_prefill_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, scale: float,
                              window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
                              head_dim: int, v_head_dim: int, requests: int, max_new: int, tokens: int, out=None,
-                             sinks=None, gate_col: int = -1):
+                             sinks=None, gate_col: int = -1, softcap: float = 0.0):
     """Attention of prompt portions (request i: rows cu_seqlens[i] .. at positions kv_offsets[i] ..) with
     score = q.k * scale - 2^(-bias_exponent (h+1) / heads) * distance under a window that keeps the first
-    `keep_first` positions; bfloat16, tensor cores, probabilities in two bfloat16 halves.  `sinks` and `gate_col`
-    as in `paged_attention_generic`."""
+    `keep_first` positions; bfloat16, tensor cores, probabilities in two bfloat16 halves.  `sinks`, `gate_col` and
+    `softcap` as in `paged_attention_generic`."""
     return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, None, None, scale,
                              window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, requests,
-                             max_new, tokens, out, sinks=sinks, gate_col=gate_col)
+                             max_new, tokens, out, sinks=sinks, gate_col=gate_col, softcap=softcap)
 
 
 def biased_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, seq_of_token, positions, scale: float,
                             window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
                             head_dim: int, v_head_dim: int, tokens: int, out=None, max_kv: int = 0, sinks=None,
-                            gate_col: int = -1):
+                            gate_col: int = -1, softcap: float = 0.0):
     """The same for token rows that each stand alone: row t is request seq_of_token[t] at position positions[t].
     `max_kv` (a bound on any row's position + 1; 0: unknown) lets rows with many visible keys be cut into runs that
     several blocks share."""
     return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, None, None, seq_of_token, positions, scale,
                              window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, tokens, 1,
-                             tokens, out, max_kv=max_kv, sinks=sinks, gate_col=gate_col)
+                             tokens, out, max_kv=max_kv, sinks=sinks, gate_col=gate_col, softcap=softcap)
 
 
 def embedding_pair(ids, positions, seq_of_token, cu_seqlens, state_slots, last_token: torch.Tensor,
@@ -945,6 +948,38 @@ def latent_prep(down: torch.Tensor, q: torch.Tensor, qa: torch.Tensor, weight: t
     _check(library().vx_latent_prep(_ptr(down), down.stride(0), _ptr(q), q.stride(0), _ptr(qa), _ptr(weight), float(eps), _ptr(inv_freq),
                                     1 if interleaved else 0, _ptr(positions), _ptr(slot_mapping), _ptr(pool), q.shape[0],
                                     heads, dim, rot_dim, rank, dtype_code(q.dtype), _stream()), "latent_prep")
+
+
+LATENT_ATTENTION_MAX_ROW = 1024
+LATENT_ATTENTION_MAX_RUNS = 16
+
+
+def latent_attention(qa: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, seq_of_token, positions, scale: float,
+                     heads: int, rank: int, rot_dim: int, max_kv: int = 0) -> torch.Tensor:
+    """Causal softmax attention of folded queries qa [tokens, heads, rank + rot_dim] over cached latent rows
+    (`pool` [pages, 1, page size, rank + rot_dim]; token row t is request seq_of_token[t] at position positions[t]):
+    score = qa . row * scale, the value is a row's first `rank` elements.  Returns [tokens, heads, rank] in qa's element
+    type.  `max_kv` (a bound on any row's position + 1; 0: unknown) lets a step of few rows cut their keys into runs
+    that several blocks share."""
+    _dev(qa, pool, block_table, seq_of_token, positions)
+    tokens, width = qa.shape[0], rank + rot_dim
+    _need(qa.is_contiguous() and tuple(qa.shape) == (tokens, heads, width) and pool.dtype == qa.dtype and pool.is_contiguous()
+          and pool.dim() == 4 and pool.shape[1] == 1 and pool.shape[3] == width,
+          "latent_attention: folded queries [T, heads, rank + rot_dim] and a pool of rows of that width")
+    _need(0 < width <= LATENT_ATTENTION_MAX_ROW, "latent_attention: rows of up to %d elements" % LATENT_ATTENTION_MAX_ROW)
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
+          "latent_attention: int32 block table [requests, blocks]")
+    blocks = tokens * (-(-heads // 8))
+    runs, scratch = 1, None
+    if max_kv > 0 and blocks < 2 * _sm_count(qa.device):
+        runs = max(1, min(LATENT_ATTENTION_MAX_RUNS, 2 * _sm_count(qa.device) // blocks, -(-max_kv // 128)))
+        if runs > 1:
+            scratch = workspace(qa.device, tokens * heads * runs * (rank + 2), which="latent_attention")
+    out = torch.empty((tokens, heads, rank), dtype=qa.dtype, device=qa.device)
+    _check(library().vx_latent_attention(_ptr(qa), _ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+                                         _ptr(positions), _ptr(out), _ptr(scratch), float(scale), tokens, heads, rank, rot_dim,
+                                         pool.shape[2], runs, dtype_code(qa.dtype), _stream()), "latent_attention")
+    return out
 
 
 def capped_gated_act(sums: torch.Tensor, bias: Optional[torch.Tensor], limit: float, slope: float,

@@ -44,7 +44,7 @@ def _mixer(cfg: KapuvikConfig, layer: dict, p: str) -> PartSpec:
                 hidden_size=cfg.width, num_heads=left["heads"], num_kv_heads=left["kv_heads"], head_dim=left["dim"],
                 v_head_dim=left["vdim"], bias=False, qk_norm=False, eps=cfg.norm_eps, scale=float(left["scale"]),
                 score_softcap=float(left.get("softcap") or 0.0), position=_rotary(left.get("rot"), left["dim"], "interleaved"),
-                names=("q", "k", "v", "o"))),
+                names=("q", "k", "v", "o"), weights_32bit=True)),
             PartSpec("decayed_linear_attention", p + "right.", dict(
                 hidden_size=cfg.width, num_heads=right["heads"], head_dim=right["dim"], v_head_dim=right["vdim"],
                 decay=list(right["decay"]), eps=cfg.norm_eps, activation="none", position=_rotary(right.get("rot"), right["dim"], "half"),

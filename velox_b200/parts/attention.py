@@ -34,7 +34,8 @@ the gate as they write a head's output.
 
 And two for designs that bound their scores and rotate neighbours: `score_softcap` c > 0 (a scaled score s becomes
 c tanh(s / c) before the softmax) and a rotary position whose `layout` is "interleaved" (channel 2i paired with
-2i + 1; the q/k kernel takes the layout as a flag).
+2i + 1; the q/k kernel takes the layout as a flag).  `weights_32bit` asks for the kernels that keep the softmax weights
+in 32 bits (two bfloat16 halves on the tensor cores) also where nothing else of the layer needs them.
 """
 from __future__ import annotations
 
@@ -73,9 +74,11 @@ class PagedAttention(Mixer):
                  keep_first: int = 0, distance_bias_exponent: float = 0.0,
                  names: Sequence[str] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight"),
                  norm_names: Sequence[str] = ("q_norm.weight", "k_norm.weight"), sink: bool = False,
-                 output_gate: bool = False, sink_name: str = "sink", gate_name: str = "g", score_softcap: float = 0.0):
+                 output_gate: bool = False, sink_name: str = "sink", gate_name: str = "g", score_softcap: float = 0.0,
+                 weights_32bit: bool = False):
         super().__init__(prefix)
         self.softcap = float(score_softcap)
+        self.weights_32bit = bool(weights_32bit)
         if self.softcap < 0:
             raise ValueError("%sscore_softcap must not be negative" % prefix)
         self.names = dict(zip(("q_proj", "k_proj", "v_proj", "o_proj"), names))
@@ -117,7 +120,7 @@ class PagedAttention(Mixer):
     def extended(self) -> bool:
         """True if the layer uses what only the kernels for biased, unequal or kept-first attention know."""
         return (self.v_head_dim != self.head_dim or self.keep_first > 0 or self.bias_exponent > 0 or self.sink
-                or self.output_gate or self.softcap > 0)
+                or self.output_gate or self.softcap > 0 or self.weights_32bit)
 
     @property
     def gate_col(self) -> int:
@@ -218,6 +221,7 @@ class PagedAttention(Mixer):
     def _attend_extended(self, qkv, ctx, cache, group) -> torch.Tensor:
         H, Hk, D = self.num_heads, self.num_kv_heads, self.head_dim
         more = dict(sinks=self.sinks, gate_col=self.gate_col)
+        capped = dict(more, softcap=self.softcap)
         page = cache.k_pool.shape[2]
         if (not ctx.decode_only and ctx.max_new >= TC_PREFILL_MIN_TOKENS and self.keep_first == 0 and self.bias_exponent == 0
                 and self.softcap == 0 and self.v_head_dim == D and ops.prefill_attention_tc_supported(qkv.dtype, D, page, H // Hk)):
@@ -226,17 +230,17 @@ class PagedAttention(Mixer):
             return ops.paged_prefill_attention_tc(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.cu_seqlens,
                                                   ctx.kv_offsets, self.scale, self.window, H, Hk, D, ctx.n_seqs, ctx.max_new,
                                                   qkv.shape[0], max_kv=ctx.max_kv, halves=True, **more)
-        if self.softcap == 0 and ops.biased_attention_supported(qkv.dtype, D, self.v_head_dim, cache.k_pool.shape[2]):
+        if ops.biased_attention_supported(qkv.dtype, D, self.v_head_dim, cache.k_pool.shape[2]):
             # a step of single tokens: every row with its own position, its keys dealt to the warps of a block
             if ctx.decode_only:
                 return ops.biased_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                    ctx.seq_of_token, ctx.positions, self.scale, self.window,
                                                    self.keep_first, self.bias_exponent, H, Hk, D, self.v_head_dim,
-                                                   qkv.shape[0], max_kv=ctx.max_kv, **more)
+                                                   qkv.shape[0], max_kv=ctx.max_kv, **capped)
             return ops.biased_prefill_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                                 ctx.cu_seqlens, ctx.kv_offsets, self.scale, self.window, self.keep_first,
                                                 self.bias_exponent, H, Hk, D, self.v_head_dim, ctx.n_seqs, ctx.max_new,
-                                                qkv.shape[0], **more)
+                                                qkv.shape[0], **capped)
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
                                            ctx.seq_of_token, ctx.positions, self.scale, self.window, H, Hk, D,
                                            qkv.shape[0], v_head_dim=self.v_head_dim, keep_first=self.keep_first,

@@ -9,7 +9,8 @@
 Only [c; r] is kept per position (`PagedLatent`: one row of kv_rank + rot_dim elements in the page).  The keys are
 never formed: since q_h . (W_uk,h c) = (W_uk,h^T q_h) . c, a step folds W_uk into its queries (one small product per
 head), attends over the cached rows as ONE key/value head of width kv_rank + rot_dim whose value is the row's first
-kv_rank elements, and raises the attended latent vector through W_uv afterwards (again one product per head).
+kv_rank elements (`ops.latent_attention`: a tile of rows is staged once for eight heads), and raises the attended latent
+vector through W_uv afterwards (again one product per head).
 Angles, the latent norm, scores and the softmax are float32.  The rotation takes either layout of the position part.
 """
 from __future__ import annotations
@@ -39,9 +40,9 @@ class LatentAttention(Mixer):
         self.scale, self.eps = float(scale), float(eps)
         if min(self.num_heads, self.head_dim, self.v_head_dim, self.kv_rank) <= 0 or self.rot_dim < 0 or self.rot_dim % 2:
             raise ValueError("%slatent attention: sizes must be positive and rot_dim even" % prefix)
-        if self.kv_rank + self.rot_dim > ops.ATTENTION_MAX_HEAD_DIM:
-            raise ValueError("%skv_rank + rot_dim = %d: the attention kernels take rows up to %d"
-                             % (prefix, self.kv_rank + self.rot_dim, ops.ATTENTION_MAX_HEAD_DIM))
+        if self.kv_rank + self.rot_dim > ops.LATENT_ATTENTION_MAX_ROW:
+            raise ValueError("%skv_rank + rot_dim = %d: the latent attention kernel takes rows up to %d"
+                             % (prefix, self.kv_rank + self.rot_dim, ops.LATENT_ATTENTION_MAX_ROW))
         self.position = build_part("position", position)
         table = self.position.rotary_table("cpu")
         if table is None or table[1] != self.rot_dim:
@@ -88,9 +89,8 @@ class LatentAttention(Mixer):
         ops.latent_prep(down, q, qa, self.norm_weight, self.eps, self.rotary[0], bool(getattr(self.position, "interleaved", False)),
                         ctx.positions, group.slot_mapping if cache.writes else None, cache.pages, H, D, R, C)
         ops.gemm_heads(q.view(t, H, D + R)[:, :, :D], self.uk_t, qa[:, :, :C])
-        latent = ops.paged_attention_generic(qa.view(t, H * (C + R)), H * (C + R), cache.k_pool, cache.v_pool, group.block_table,
-                                             ctx.seq_of_token, ctx.positions, self.scale, 0, H, 1, C + R, t,
-                                             v_head_dim=C, v_stride=C + R)
+        latent = ops.latent_attention(qa, cache.pages, group.block_table, ctx.seq_of_token, ctx.positions, self.scale, H, C, R,
+                                      max_kv=ctx.max_kv)
         o = torch.empty((t, H, Dv), dtype=x.dtype, device=x.device)
-        ops.gemm_heads(latent.view(t, H, C), self.uv, o)
+        ops.gemm_heads(latent, self.uv, o)
         return self.out(o.view(t, H * Dv))
