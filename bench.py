@@ -681,11 +681,14 @@ def kapuvik_kernels(pk, sz):
     lin_fl = T * HL * 2.0 * (32 * 2 * D + 2 * D * D)
     sb = B * HL * D * D * 4 * 2.0
     inv_r = (1e4 ** (-torch.arange(0, 64, 2, device=dev, dtype=torch.float32) / 64)).contiguous()
-    row("prompt linear attention, decay per channel (float32 operands)", us(lambda: ops.linear_attention_walk(
-        x, 0, HL * D, 2 * HL * D, state, cu, slot0, 1, HL, D, D, gate=gate, gate_mul=1 / 16.0, q_mul=D ** -0.5), 5), lin_fl)
-    row("prompt linear attention, rotated, fixed decay (float32 operands)", us(lambda: ops.linear_attention_walk(
+    plan = ops.StretchPlan([T], dev)
+    row("prompt linear attention, decay per channel (float32 operands, stretches side by side)", us(lambda: ops.linear_attention_walk(
+        x, 0, HL * D, 2 * HL * D, state, cu, slot0, 1, HL, D, D, gate=gate, gate_mul=1 / 16.0, q_mul=D ** -0.5, stretches=plan), 5), lin_fl)
+    row("prompt linear attention, rotated, fixed decay (float32 operands, stretches side by side)", us(lambda: ops.linear_attention_walk(
         x, 0, HL * D, 2 * HL * D, state, cu, slot0, 1, HL, D, D, decay=decay, inv_freq=inv_r, rot_dim=64, positions=pos_t,
-        k_mul=D ** -0.5), 5), lin_fl)
+        k_mul=D ** -0.5, stretches=plan), 5), lin_fl)
+    row("prompt linear attention, decay per channel, in order (one walk)", us(lambda: ops.linear_attention_walk(
+        x, 0, HL * D, 2 * HL * D, state, cu, slot0, 1, HL, D, D, gate=gate, gate_mul=1 / 16.0, q_mul=D ** -0.5), 3), lin_fl)
     row("prompt linear attention, Dobepel (chunks side by side, mma.sync, halves)", us(lambda: ops.linear_attention(
         x, 0, HL * D, 2 * HL * D, decay, state, cu, slot0, 1, T, HL, D, D)), lin_fl)
     posd = ints([CTX - 1] * B)

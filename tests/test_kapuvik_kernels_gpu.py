@@ -236,6 +236,59 @@ def test_the_state_walk_with_a_decay_per_channel_and_position(dtype, H, D, Dv, t
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("per_channel", [False, True])
+def test_stretches_walked_side_by_side_give_what_the_walk_in_order_gives(dtype, per_channel):
+    """Three requests of 300, 1 and 77 rows whose states are not zero, cut into stretches of 64 and of 16 rows: the outputs
+    and the states left in the slots are the plain walk's (with a rotation and multipliers for the decay per head)."""
+    from velox_b200.csrc import ops
+    rng = np.random.default_rng(8)
+    H, D, Dv, lens = 2, 12, 20, [300, 1, 77]
+    T = sum(lens)
+    x, q, k, v = walk_case(rng, T, H, D, Dv)
+    x = 0.5 * x
+    q, k, v = 0.5 * q, 0.5 * k, 0.5 * v
+    x = bf(x)
+    q, k, v = (x[:, :H * D].reshape(T, H, D), x[:, H * D:2 * H * D].reshape(T, H, D), x[:, 2 * H * D:].reshape(T, H, Dv))
+    start = rng.normal(size=(4, H, D, Dv))
+    slots, offs = [2, 0, 3], [40, 7, 0]
+    pos = np.concatenate([np.arange(o, o + n) for o, n in zip(offs, lens)])
+    z = rng.normal(1.0, 1.5, size=(T, H * D))
+    decay = np.array([0.9, 0.99])
+    want_o, want_s = [], {}
+    row = 0
+    for n, slot in zip(lens, slots):
+        sl = slice(row, row + n)
+        if per_channel:
+            qq, kk = q[sl] * D ** -0.5, k[sl]
+            a = (K.sigmoid(z[sl]) ** (1.0 / 5.0)).reshape(n, H, D)
+        else:
+            qq = K.rotate(q[sl], pos[sl], 100.0, 8, False)
+            kk = K.rotate(k[sl], pos[sl], 100.0, 8, False) * 0.3
+            a = np.broadcast_to(decay[None, :, None], (n, H, D))
+        S = start[slot].copy()
+        out = np.zeros((n, H, Dv))
+        for t in range(n):
+            S = a[t][:, :, None] * S + kk[t][:, :, None] * v[sl][t][:, None, :]
+            out[t] = np.einsum("hdv,hd->hv", S, qq[t])
+        want_o.append(out.reshape(n, H * Dv))
+        want_s[slot] = S
+        row += n
+    want_o = np.concatenate(want_o)
+    cu = ints(np.concatenate([[0], np.cumsum(lens)]))
+    for length in (64, 16):
+        state = dev(start)
+        plan = ops.StretchPlan(lens, DEV, length)
+        assert plan.count == sum(-(-n // length) for n in lens)
+        more = (dict(gate=dev(z), gate_mul=1.0 / 5.0, q_mul=D ** -0.5) if per_channel else
+                dict(decay=dev(decay), inv_freq=inv_freq(100.0, 8), rot_dim=8, positions=ints(pos), k_mul=0.3))
+        got = ops.linear_attention_walk(dev(x, dtype), 0, H * D, 2 * H * D, state, cu, ints(slots), 3, H, D, Dv, stretches=plan, **more)
+        close(got, want_o, 1e-4)
+        for slot, S in want_s.items():
+            close(state[slot], S, 1e-4)
+        assert torch.equal(state[1], dev(start)[1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,Dv,weight,act", [(3, 24, True, "silu"), (2, 14, False, "silu"), (2, 64, True, "sigmoid")])
 def test_every_head_is_normed_by_itself_and_gated(dtype, H, Dv, weight, act):
     from velox_b200.csrc import ops

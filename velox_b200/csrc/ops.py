@@ -101,6 +101,9 @@ def _declare(lib) -> None:
         "vx_paged_attention_generic_cap": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P, I, F, I, P],
         "vx_gemm_nt_simt_batched": [P, P, P, P, I, I, I, I, I, I, I, c_longlong, c_longlong, c_longlong, I, I, P],
         "vx_linear_attention_walk": [P, I, I, I, I, P, P, I, F, P, I, I, P, F, F, P, P, P, P, I, I, I, I, I, P],
+        "vx_linear_attention_walk_parts": [P, I, I, I, I, P, P, I, F, P, I, I, P, F, F, P, P, P, P, I, I, I, I, I, I, P],
+        "vx_stretch_log_decay": [P, I, F, P, P, I, I, P],
+        "vx_stretch_scan": [P, P, P, P, P, P, P, I, I, I, I, P],
         "vx_head_norm_gate": [P, P, I, P, P, I, I, I, F, I, I, P],
         "vx_latent_prep": [P, I, P, I, P, P, F, P, I, P, P, P, I, I, I, I, I, I, P],
         "vx_capped_gated_act": [P, P, P, I, I, F, F, I, P],
@@ -882,15 +885,42 @@ def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Ten
     return out
 
 
+STRETCH_MIN_TOKENS = 128    # a step's longest portion from which its tokens are walked in stretches side by side
+STRETCH_MIN_LENGTH = 64
+STRETCH_MOST = 64           # stretches of a step, about: longer steps get longer stretches
+
+
+class StretchPlan:
+    """A step's token rows cut into stretches of at most `length` rows that never cross a request: `cu` [stretches + 1]
+    first row of each, `first` [requests + 1] first stretch of each request, `ident` 0 .. stretches - 1 (int32, on the
+    device)."""
+
+    def __init__(self, new_lens, device, length: int = 0):
+        total = int(sum(new_lens))
+        self.length = int(length) or max(STRETCH_MIN_LENGTH, -(-(-(-total // STRETCH_MOST)) // 16) * 16)
+        cu, first, row = [0], [0], 0
+        for n in new_lens:
+            for lo in range(0, int(n), self.length):
+                cu.append(row + min(int(n), lo + self.length))
+            row += int(n)
+            first.append(len(cu) - 1)
+        self.count, self.requests = len(cu) - 1, len(new_lens)
+        both = torch.tensor(cu + first + list(range(self.count)), dtype=torch.int32).to(device, non_blocking=True)
+        self.cu, self.first = both[:len(cu)], both[len(cu):len(cu) + len(first)]
+        self.ident = both[len(cu) + len(first):]
+
+
 def linear_attention_walk(x: torch.Tensor, q_col: int, k_col: int, v_col: int, state: torch.Tensor, cu_seqlens, state_slots,
                           seqs: int, heads: int, dim: int, vdim: int, decay: Optional[torch.Tensor] = None,
                           gate: Optional[torch.Tensor] = None, gate_mul: float = 1.0, inv_freq: Optional[torch.Tensor] = None,
                           rot_dim: int = 0, interleaved: bool = False, positions: Optional[torch.Tensor] = None,
-                          q_mul: float = 1.0, k_mul: float = 1.0) -> torch.Tensor:
+                          q_mul: float = 1.0, k_mul: float = 1.0, stretches: Optional[StretchPlan] = None) -> torch.Tensor:
     """Per head S = a (.) S + k v^T, o = S^T q over every request's tokens in order, a = decay[h] (float32 per head) or
     sigmoid(gate)^gate_mul per key channel and token (`gate` float32 [tokens, heads * dim], contiguous rows).  q and k
     are turned by position * inv_freq on their first `rot_dim` channels, then multiplied by q_mul / k_mul, all in
-    float32.  `state` float32 [slots, heads, dim, vdim] is read and written back.  Returns float32 [tokens, heads * vdim]."""
+    float32.  `state` float32 [slots, heads, dim, vdim] is read and written back.  Returns float32 [tokens, heads * vdim].
+    With `stretches` (the plan of this step's rows) the stretches are walked side by side: once from zero for what each
+    adds to the state, a scan over a request's stretches for the state at the start of each, and once more for the outputs."""
     _dev(x, decay, gate, inv_freq, positions, state, cu_seqlens, state_slots)
     _need(x.stride(1) == 1 and (decay is None) != (gate is None), "linear_attention_walk: a decay per head or a gate per channel")
     if decay is not None:
@@ -904,11 +934,30 @@ def linear_attention_walk(x: torch.Tensor, q_col: int, k_col: int, v_col: int, s
     _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim),
           "linear_attention_walk: float32 state [slots, heads, dim, vdim]")
     out = torch.empty((x.shape[0], heads * vdim), dtype=torch.float32, device=x.device)
-    _check(library().vx_linear_attention_walk(
-        _ptr(x), x.stride(0), int(q_col), int(k_col), int(v_col), _ptr(decay), _ptr(gate), gate.stride(0) if gate is not None else 0,
-        float(gate_mul), _ptr(inv_freq), int(rot_dim) if inv_freq is not None else 0, 1 if interleaved else 0, _ptr(positions),
-        float(q_mul), float(k_mul), _ptr(state), _ptr(cu_seqlens), _ptr(state_slots), _ptr(out), int(seqs), heads, dim, vdim,
-        dtype_code(x.dtype), _stream()), "linear_attention_walk")
+    lib = library()
+
+    def walk(st, cu, slots, n, result, fresh):
+        _check(lib.vx_linear_attention_walk_parts(
+            _ptr(x), x.stride(0), int(q_col), int(k_col), int(v_col), _ptr(decay), _ptr(gate), gate.stride(0) if gate is not None else 0,
+            float(gate_mul), _ptr(inv_freq), int(rot_dim) if inv_freq is not None else 0, 1 if interleaved else 0, _ptr(positions),
+            float(q_mul), float(k_mul), _ptr(st), _ptr(cu), _ptr(slots), _ptr(result), int(n), heads, dim, vdim,
+            1 if fresh else 0, dtype_code(x.dtype), _stream()), "linear_attention_walk")
+
+    if stretches is None:
+        walk(state, cu_seqlens, state_slots, seqs, out, False)
+        return out
+    _need(stretches.requests == seqs, "linear_attention_walk: the stretches are those of another step")
+    per = heads * dim * vdim
+    parts = workspace(x.device, stretches.count * per, which="stretch_parts")
+    log_a = None
+    if gate is not None:
+        log_a = workspace(x.device, stretches.count * heads * dim, which="stretch_decay")
+        _check(lib.vx_stretch_log_decay(_ptr(gate), gate.stride(0), float(gate_mul), _ptr(stretches.cu), _ptr(log_a),
+                                        stretches.count, heads * dim, _stream()), "stretch_log_decay")
+    walk(parts, stretches.cu, stretches.ident, stretches.count, None, True)
+    _check(lib.vx_stretch_scan(_ptr(parts), _ptr(state), _ptr(log_a), _ptr(decay), _ptr(stretches.cu), _ptr(stretches.first),
+                               _ptr(state_slots), seqs, heads, dim, vdim, _stream()), "stretch_scan")
+    walk(parts, stretches.cu, stretches.ident, stretches.count, out, False)
     return out
 
 

@@ -3,6 +3,7 @@
 //   linear_attention_walk   S_p = a_p (.) S_(p-1) + k_p v_p^T, o_p = S_p^T q_p with the decay a number per
 //                           head or a number per key channel and position; q and k optionally rotated by
 //                           position and multiplied by numbers on the way in
+//   stretch_log_decay, stretch_scan   a long portion cut into stretches that are walked side by side
 //   head_norm_gate          every head's output divided by its root mean square (optionally times a
 //                           weight shared by the heads), times silu or sigmoid of a gate projection
 //   latent_prep             the down-projected row of a latent attention: norm of the latent part, rotation
@@ -34,7 +35,7 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
                              const float* __restrict__ inv_freq, int rot_dim, int interleaved,
                              const int* __restrict__ positions, float q_mul, float k_mul, float* __restrict__ state,
                              const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
-                             float* __restrict__ out, int H, int D, int Dv) {
+                             float* __restrict__ out, int H, int D, int Dv, int fresh) {
     extern __shared__ float smem[];
     float* q_s = smem;                       // [LW_CHUNK][D]
     float* k_s = q_s + LW_CHUNK * D;         // [LW_CHUNK][D]
@@ -54,7 +55,7 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
 #pragma unroll
     for (int i = 0; i < DR; ++i) {
         const int d = slice + LW_SLICES * i;
-        S[i] = (live && d < D) ? st[(size_t)d * Dv + c] : 0.f;
+        S[i] = (live && d < D && !fresh) ? st[(size_t)d * Dv + c] : 0.f;
     }
     for (int tb = t0; tb < t1; tb += LW_CHUNK) {
         const int n = min(LW_CHUNK, t1 - tb);
@@ -105,7 +106,7 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
             }
             o += __shfl_xor_sync(0xffffffffu, o, 1);
             o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (slice == 0 && live) out[(size_t)(tb + tt) * H * Dv + (size_t)h * Dv + c] = o;
+            if (slice == 0 && live && out) out[(size_t)(tb + tt) * H * Dv + (size_t)h * Dv + c] = o;
         }
     }
 #pragma unroll
@@ -120,7 +121,7 @@ static int launch_linear_attention_walk(const T* x, int ldx, int q_col, int k_co
                                         const float* gate, int ldg, float gate_mul, const float* inv_freq, int rot_dim,
                                         int interleaved, const int* positions, float q_mul, float k_mul, float* state,
                                         const int* cu_seqlens, const int* state_slots, float* out, int seqs, int H, int D,
-                                        int Dv, cudaStream_t stream) {
+                                        int Dv, int fresh, cudaStream_t stream) {
     dim3 grid((Dv + LW_COLS - 1) / LW_COLS, H, seqs);
     const size_t smem = sizeof(float) * LW_CHUNK * ((gate ? 3 : 2) * D + LW_COLS);
     const int dr = (D + LW_SLICES - 1) / LW_SLICES;
@@ -130,7 +131,7 @@ static int launch_linear_attention_walk(const T* x, int ldx, int q_col, int k_co
         if (int rc = vx_configure_smem(linear_attention_walk_kernel<T, DR>, LW_MAX_SMEM, configured[SLOT])) return rc;          \
         VX_LAUNCH_K(VX_K_ATTENTION, (linear_attention_walk_kernel<T, DR>), grid, LW_COLS * LW_SLICES, smem, stream, x,  \
                     ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul, inv_freq, rot_dim, interleaved, positions,    \
-                    q_mul, k_mul, state, cu_seqlens, state_slots, out, H, D, Dv);                                       \
+                    q_mul, k_mul, state, cu_seqlens, state_slots, out, H, D, Dv, fresh);                                \
     } while (0)
     if (dr <= 8) LW_GO(8, 0);
     else if (dr <= 16) LW_GO(16, 1);
@@ -142,12 +143,13 @@ static int launch_linear_attention_walk(const T* x, int ldx, int q_col, int k_co
 }
 
 // x: rows with q, k [H, D] and v [H, Dv] at the given columns.  decay [H] or gate [tokens, ldg] (float32; one
-// of the two).  state float32 [slot, H, D, Dv], read and written back.  out float32 [tokens, H * Dv].
-extern "C" int vx_linear_attention_walk(const void* x, int ldx, int q_col, int k_col, int v_col, const float* decay,
-                                        const float* gate, int ldg, float gate_mul, const float* inv_freq, int rot_dim,
-                                        int interleaved, const int* positions, float q_mul, float k_mul, float* state,
-                                        const int* cu_seqlens, const int* state_slots, float* out, int seqs, int H,
-                                        int D, int Dv, int dtype, cudaStream_t stream) {
+// of the two).  state float32 [slot, H, D, Dv], read (from zero instead with `fresh`) and written back.  out float32
+// [tokens, H * Dv], or null where only the states are wanted.
+extern "C" int vx_linear_attention_walk_parts(const void* x, int ldx, int q_col, int k_col, int v_col, const float* decay,
+                                              const float* gate, int ldg, float gate_mul, const float* inv_freq, int rot_dim,
+                                              int interleaved, const int* positions, float q_mul, float k_mul, float* state,
+                                              const int* cu_seqlens, const int* state_slots, float* out, int seqs, int H,
+                                              int D, int Dv, int fresh, int dtype, cudaStream_t stream) {
     if (seqs <= 0) return VX_OK;
     if (H <= 0 || D <= 0 || Dv <= 0 || D > 256 || q_col < 0 || k_col < 0 || v_col < 0) return VX_ERR_SHAPE;
     if ((decay == nullptr) == (gate == nullptr)) return VX_ERR_SHAPE;
@@ -157,12 +159,91 @@ extern "C" int vx_linear_attention_walk(const void* x, int ldx, int q_col, int k
     if (dtype == VX_F32)
         return launch_linear_attention_walk<float>((const float*)x, ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul,
                                                    inv_freq, rot_dim, interleaved, positions, q_mul, k_mul, state,
-                                                   cu_seqlens, state_slots, out, seqs, H, D, Dv, stream);
+                                                   cu_seqlens, state_slots, out, seqs, H, D, Dv, fresh, stream);
     if (dtype == VX_BF16)
         return launch_linear_attention_walk<bf16>((const bf16*)x, ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul,
                                                   inv_freq, rot_dim, interleaved, positions, q_mul, k_mul, state,
-                                                  cu_seqlens, state_slots, out, seqs, H, D, Dv, stream);
+                                                  cu_seqlens, state_slots, out, seqs, H, D, Dv, fresh, stream);
     return VX_ERR_DTYPE;
+}
+
+extern "C" int vx_linear_attention_walk(const void* x, int ldx, int q_col, int k_col, int v_col, const float* decay,
+                                        const float* gate, int ldg, float gate_mul, const float* inv_freq, int rot_dim,
+                                        int interleaved, const int* positions, float q_mul, float k_mul, float* state,
+                                        const int* cu_seqlens, const int* state_slots, float* out, int seqs, int H,
+                                        int D, int Dv, int dtype, cudaStream_t stream) {
+    if (!out) return VX_ERR_SHAPE;
+    return vx_linear_attention_walk_parts(x, ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul, inv_freq, rot_dim,
+                                          interleaved, positions, q_mul, k_mul, state, cu_seqlens, state_slots, out, seqs, H,
+                                          D, Dv, 0, dtype, stream);
+}
+
+// A long portion walked in stretches side by side.  With every stretch's own contribution S_loc[c] (the walk from a zero
+// state, `fresh`) and the decay over the whole stretch A_c (per head, or per key channel), the state at a stretch's start
+// follows from the one before it: S_start[c + 1] = diag(A_c) S_start[c] + S_loc[c]; a second walk of every stretch from its
+// start state gives the outputs.  Two kernels around the walks:
+//   stretch_log_decay  log A_c [stretch, H D] = sum over the stretch's tokens of gate_mul * log_sigmoid(gate)
+//   stretch_scan       per request, in the order of its stretches: parts[c] (holding S_loc[c]) takes S_start[c]; the state
+//                      slot takes the state after the last stretch.  One thread per state element.
+__global__ void stretch_log_decay_kernel(const float* __restrict__ gate, int ldg, float gate_mul,
+                                         const int* __restrict__ cu_stretch, float* __restrict__ log_a, int HD) {
+    pdl_wait();
+    pdl_trigger();
+    const int c = blockIdx.y, i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= HD) return;
+    float sum = 0.f;
+    for (int t = cu_stretch[c]; t < cu_stretch[c + 1]; ++t) sum += gate_mul * log_sigmoid(gate[(size_t)t * ldg + i]);
+    log_a[(size_t)c * HD + i] = sum;
+}
+
+__global__ void stretch_scan_kernel(float* __restrict__ parts, float* __restrict__ state, const float* __restrict__ log_a,
+                                    const float* __restrict__ decay, const int* __restrict__ cu_stretch,
+                                    const int* __restrict__ first_stretch, const int* __restrict__ state_slots, int H, int D,
+                                    int Dv) {
+    pdl_wait();
+    pdl_trigger();
+    const int seq = blockIdx.y;
+    const size_t per = (size_t)H * D * Dv;
+    const size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= per) return;
+    const int hd = (int)(e / Dv), h = hd / D;
+    float* st = state + (size_t)state_slots[seq] * per + e;
+    float S = *st;
+    const float l2 = decay ? log2f(decay[h]) : 0.f;
+    for (int c = first_stretch[seq]; c < first_stretch[seq + 1]; ++c) {
+        float* p = parts + (size_t)c * per + e;
+        const float loc = *p;
+        *p = S;
+        const float a = log_a ? expf(log_a[(size_t)c * H * D + hd]) : exp2f((float)(cu_stretch[c + 1] - cu_stretch[c]) * l2);
+        S = fmaf(a, S, loc);
+    }
+    *st = S;
+}
+
+extern "C" int vx_stretch_log_decay(const float* gate, int ldg, float gate_mul, const int* cu_stretch, float* log_a,
+                                    int stretches, int HD, cudaStream_t stream) {
+    if (stretches <= 0) return VX_OK;
+    if (HD <= 0 || ldg < HD) return VX_ERR_SHAPE;
+    if (stretches > 65535) return VX_ERR_LIMIT;
+    VX_LAUNCH_K(VX_K_ELEMENTWISE, stretch_log_decay_kernel, dim3((HD + 127) / 128, stretches), 128, 0, stream, gate, ldg,
+                gate_mul, cu_stretch, log_a, HD);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}
+
+// parts float32 [stretch, H, D, Dv]; log_a [stretch, H D] or null with decay [H]; the stretches of request i are
+// first_stretch[i] .. first_stretch[i + 1] - 1, stretch c holds token rows cu_stretch[c] .. cu_stretch[c + 1] - 1.
+extern "C" int vx_stretch_scan(float* parts, float* state, const float* log_a, const float* decay, const int* cu_stretch,
+                               const int* first_stretch, const int* state_slots, int seqs, int H, int D, int Dv,
+                               cudaStream_t stream) {
+    if (seqs <= 0) return VX_OK;
+    if (H <= 0 || D <= 0 || Dv <= 0 || ((log_a == nullptr) == (decay == nullptr))) return VX_ERR_SHAPE;
+    const size_t per = (size_t)H * D * Dv;
+    if (seqs > 65535 || (per + 255) / 256 > 0x7fffffffULL) return VX_ERR_LIMIT;
+    VX_LAUNCH_K(VX_K_ELEMENTWISE, stretch_scan_kernel, dim3((unsigned)((per + 255) / 256), seqs), 256, 0, stream, parts, state,
+                log_a, decay, cu_stretch, first_stretch, state_slots, H, D, Dv);
+    VX_LAUNCH_CHECK();
+    return VX_OK;
 }
 
 // One warp per (token, head): out = o / sqrt(mean(o^2) + eps) (* w[d]) * act(g), act = sigmoid (0) or silu (1).

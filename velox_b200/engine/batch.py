@@ -59,6 +59,9 @@ class StepContext:
     # (residual, its rounding to the engine's element type) as the embedding or the last block left it, for a
     # block whose sublayers read the stream itself; valid for the next block only (the model's loop drops it)
     rounded: Optional[tuple] = None
+    # the step's rows cut into stretches for recurrences that walk a long portion's stretches side by side; made by the
+    # first mixer that wants it
+    walk_stretches: Optional[object] = None
 
     @property
     def decode_only(self) -> bool:

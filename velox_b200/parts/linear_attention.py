@@ -18,7 +18,9 @@ fixed-decay form has three kernels (`ops.linear_attention`, `csrc/linear_attenti
 token, chunks of 64 tokens on the tensor cores one after the other, and all chunks side by side with a scan.  With a
 rotation, multipliers or a decay per channel the recurrence of `csrc/state_mixers.cu` runs (`ops.linear_attention_walk`):
 rotation angles, multipliers, decays (through their logarithm), state and outputs are float32 there, q, k, v enter as
-the projection left them.  Norms and gates are float32.
+the projection left them.  A step with a portion of 128 tokens or more cuts its rows into stretches (64 tokens, longer in
+long steps) that are walked side by side: once from zero for what each adds to the state, a scan over a request's stretches
+for the state at the start of each, once more for the outputs (`ops.StretchPlan`).  Norms and gates are float32.
 """
 from __future__ import annotations
 
@@ -76,6 +78,17 @@ class _LinearAttention(Mixer):
 
     def cache_spec(self):
         return FixedState((self.num_heads, self.head_dim, self.v_head_dim), "float32")
+
+    @staticmethod
+    def _stretches(ctx):
+        """The step's rows cut into stretches that the recurrence walks side by side, from a portion of
+        `ops.STRETCH_MIN_TOKENS` rows on; made once a step and kept on its context."""
+        if ctx.max_new < ops.STRETCH_MIN_TOKENS or len(ctx.new_lens) != ctx.n_seqs:
+            return None
+        plan = getattr(ctx, "walk_stretches", None)
+        if plan is None:
+            plan = ctx.walk_stretches = ops.StretchPlan(ctx.new_lens, ctx.positions.device)
+        return plan
 
     def _finish(self, o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
         """o float32 [tokens, heads * vdim] -> normed, gated, projected."""
@@ -135,7 +148,8 @@ class DecayedLinearAttention(_LinearAttention):
             o = ops.linear_attention_walk(x, 0, H * D, 2 * H * D, cache.state, ctx.cu_seqlens, ctx.state_slots, ctx.n_seqs,
                                           H, D, Dv, decay=self.decay, inv_freq=inv_freq, rot_dim=rot,
                                           interleaved=bool(getattr(self.position, "interleaved", False)),
-                                          positions=ctx.positions, q_mul=self.q_scale, k_mul=self.k_scale)
+                                          positions=ctx.positions, q_mul=self.q_scale, k_mul=self.k_scale,
+                                          stretches=self._stretches(ctx))
         return self._finish(o, x[:, 2 * H * D + H * Dv:2 * H * D + 2 * H * Dv])
 
 
@@ -179,5 +193,5 @@ class GatedLinearAttention(_LinearAttention):
         g0 = 2 * H * D + H * Dv
         z = self.decay_up(x[:, g0 + H * Dv:g0 + H * Dv + self.decay_rank], torch.float32)   # float32 sums plus the bias
         o = ops.linear_attention_walk(x, 0, H * D, 2 * H * D, cache.state, ctx.cu_seqlens, ctx.state_slots, ctx.n_seqs,
-                                      H, D, Dv, gate=z, gate_mul=1.0 / self.tau, q_mul=self.q_scale)
+                                      H, D, Dv, gate=z, gate_mul=1.0 / self.tau, q_mul=self.q_scale, stretches=self._stretches(ctx))
         return self._finish(o, x[:, g0:g0 + H * Dv])
