@@ -659,6 +659,18 @@ def kapuvik_kernels(pk, sz):
     lnb = B * CTX * (C + R) * 2.0
     row("prompt latent attention (folded queries over cached rows)", us(lambda: ops.latent_attention(
         qa, lp, bt, seq_t, pos_t, 192 ** -0.5, H, C, R, max_kv=T), 3), lfl)
+    if ops.raised_attention_supported(bf, D + R, D):
+        # the same prompt the other way round: rows gathered out of the pages, keys and values raised by one product, the
+        # tensor-core prompt kernel on them (heads of D + R keys and D values); FLOPs of the raised form
+        plan = ops.RaisedPlan([T], dev)
+        w_raise = (torch.randn((H * (2 * D + R), C + R), device=dev) * 0.05).to(bf)
+        qr = torch.randn((T, H * (D + R)), device=dev).to(bf)
+        rfl = 2.0 * (T * (T + 1) // 2) * (2 * D + R) * H
+        kv_rows = ops.gemm_bf16(ops.latent_gather(lp, bt, cu, off, plan), w_raise)
+        row("prompt latent attention, raised: tensor-core kernel on raised rows (keys of %d, values of %d)" % (D + R, D), us(
+            lambda: ops.raised_attention(qr, qr.shape[1], kv_rows, cu, off, plan, 192 ** -0.5, H, D + R, D, T)), rfl)
+        row("prompt latent attention, raised: gather of %d cached rows + product that raises them" % T, us(
+            lambda: ops.gemm_bf16(ops.latent_gather(lp, bt, cu, off, plan), w_raise)), 2.0 * T * (C + R) * H * (2 * D + R))
     row("decode latent attention", us(lambda: ops.latent_attention(
         qad, lp, bt, seqs, pos, 192 ** -0.5, H, C, R, max_kv=CTX), 20), 0.0, lnb)
     down, qq = torch.randn((T, C + R), device=dev).to(bf), torch.randn((T, H * (D + R)), device=dev).to(bf)

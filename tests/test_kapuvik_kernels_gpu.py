@@ -173,6 +173,62 @@ def test_latent_rows_are_prepared_cached_and_attended_as_the_plain_mixer_does(dt
         close(row[C:], k_rot[j, 0], TOL[dtype])
 
 
+@pytest.mark.parametrize("H,D,R,Dv,C", [(3, 32, 64, 32, 40), (2, 64, 32, 64, 72), (5, 128, 64, 128, 96), (2, 32, 32, 64, 24)])
+def test_raised_keys_and_values_under_the_tensor_core_prompt_kernel(H, D, R, Dv, C):
+    """Two requests of unequal length in two steps each (the second step reads rows that the first cached, and is cut in the
+    middle of a page and of a block of raised rows): the cached rows gathered out of scattered pages, one product that leaves
+    every head's key and value side by side, the prompt kernel on those rows with the queries turned where they lie.
+    Request b's first key is made to stand out for its last query, far behind it."""
+    from velox_b200.csrc import ops
+    rng = np.random.default_rng(12)
+    S, base, scale, dtype = 16, 300.0, 0.15, torch.bfloat16
+    lens, cuts = [150, 83], [70, 37]
+    n_pages = 20
+    pages = np.random.default_rng(13).permutation(n_pages)
+    tables = [pages[:10], pages[10:16]]
+    wn, uk, uv = bf(1.0 + 0.2 * rng.normal(size=C)), bf(rng.normal(size=(H * D, C)) / np.sqrt(C)), bf(rng.normal(size=(H * Dv, C)) / np.sqrt(C))
+    w_raise = np.zeros((H, D + R + Dv, C + R))
+    w_raise[:, :D, :C] = uk.reshape(H, D, C)
+    w_raise[:, D:D + R, C:] = np.eye(R)
+    w_raise[:, D + R:, :C] = uv.reshape(H, Dv, C)
+    w_raise = dev(w_raise.reshape(-1, C + R), dtype)
+    q = [bf(rng.normal(size=(n, H, D + R))) for n in lens]
+    down = [bf(rng.normal(size=(n, C + R))) for n in lens]
+    down[1][0, C:] *= 6.0           # the shared rotated part of request b's first key, and the last query's rotated part
+    q[1][-1, :, D:] = bf(K.rotate(down[1][:1, None, C:], np.array([-(lens[1] - 1)]), base, R, True)[0])   # (turned back: it meets key 0)
+    want = []
+    for n, qq, dd in zip(lens, q, down):
+        pos = np.arange(n)
+        c = K.rms(dd[:, :C], 1e-5) * wn
+        k_rot = K.rotate(dd[:, None, C:], pos, base, R, True)
+        q_rot = K.rotate(qq[:, :, D:], pos, base, R, True)
+        kk = np.concatenate([(c @ uk.T).reshape(n, H, D), np.broadcast_to(k_rot, (n, H, R))], axis=2)
+        want.append(K.causal_softmax_attention(np.concatenate([qq[:, :, :D], q_rot], axis=2), kk, (c @ uv.T).reshape(n, H, Dv), scale))
+    pool = torch.full((n_pages, 1, S, C + R), float("nan"), dtype=dtype, device=DEV)
+    bt = torch.full((2, 12), -1, dtype=torch.int32, device=DEV)
+    for i, t in enumerate(tables):
+        bt[i, :len(t)] = ints(t)
+    fr = inv_freq(base, R)
+    got = [[], []]
+    for step in range(2):
+        spans = [(0, c) if step == 0 else (c, n) for c, n in zip(cuts, lens)]
+        x = dev(np.concatenate([np.concatenate([q[i][lo:hi].reshape(hi - lo, -1), down[i][lo:hi]], axis=1) for i, (lo, hi) in enumerate(spans)]), dtype)
+        pos = [j for lo, hi in spans for j in range(lo, hi)]
+        slots = [int(tables[i][j // S]) * S + j % S for i, (lo, hi) in enumerate(spans) for j in range(lo, hi)]
+        news = [hi - lo for lo, hi in spans]
+        cu, off = ints([0, news[0], news[0] + news[1]]), ints([lo for lo, _ in spans])
+        ops.latent_prep(x[:, H * (D + R):], x[:, :H * (D + R)], None, dev(wn), 1e-5, fr, True, ints(pos), ints(slots), pool, H, D, R, C)
+        plan = ops.RaisedPlan([hi for _, hi in spans], DEV)
+        rows = ops.latent_gather(pool, bt, cu, off, plan)
+        assert rows.shape[0] == sum(-(-hi // 64) * 64 for _, hi in spans) and torch.isfinite(rows.float()).all()
+        kv = ops.gemm_bf16(rows, w_raise)
+        o = ops.raised_attention(x, x.shape[1], kv, cu, off, plan, scale, H, D + R, Dv, max(news))
+        got[0].append(o[:news[0]])
+        got[1].append(o[news[0]:])
+    for i in range(2):
+        close(torch.cat(got[i]).view(lens[i], H, Dv), want[i], 3 * TOL[dtype])
+
+
 def walk_case(rng, T, H, D, Dv, extra=0):
     x = bf(rng.normal(size=(T, 2 * H * D + H * Dv + extra)))
     return x, x[:, :H * D].reshape(T, H, D), x[:, H * D:2 * H * D].reshape(T, H, D), x[:, 2 * H * D:2 * H * D + H * Dv].reshape(T, H, Dv)

@@ -36,6 +36,20 @@
 // The least power of two that is not below n (n >= 4 here: heads of at least 32 elements).
 __host__ __device__ constexpr int ab_pow2(int n) { return n <= 4 ? 4 : (n <= 8 ? 8 : 16); }
 
+// A row's chunks of 16 bytes in shared memory: rows of whole groups of 8 chunks lie as they are (the XOR below stays inside
+// a group), the others are padded to a power of two.
+__host__ __device__ constexpr int ab_chunks(int n) { return n % 8 == 0 ? n : ab_pow2(n); }
+
+// Where keys and values lie, in elements: key j of kv head hk of a request is at
+//   k + page * k_page + hk * k_head + (j % S) * k_row,   page = table[j / S]
+// (a page pool [pages, kv heads, S, size] has k_page = Hk S size, k_head = S size, k_row = size; rows [n, heads, sizes]
+// that a matrix product left have k_row = the row's length and k_head = one head's share of it).  With `table_by_segment`
+// the block table's row is the segment's number, not the request's.
+struct AbLayout {
+    long long k_page, k_head, k_row, v_page, v_head, v_row;
+    int table_by_segment;
+};
+
 template <int CH> __device__ __forceinline__ int ab_swz(int r, int cc) {
     // 16-byte chunk cc of row r; rows of 8 or 16 chunks XOR the row's low bits, rows of 4 chunks
     // (two rows to a 128-byte line) every second row's
@@ -68,6 +82,7 @@ struct AbSegments {
     const int* kv_offsets;    //           at positions kv_offsets[s] ..
     const int* seq_of_token;  // single tokens: segment s is token row s of request seq_of_token[s]
     const int* positions;     //           at position positions[s]
+    const int* seq_list;      // portions: segment s is request seq_list[s] (null: request s)
 };
 
 template <int DK, int DV>
@@ -76,10 +91,10 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
                         const bf16* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
                         AbSegments seg, bf16* __restrict__ out, int out_row_stride, float scale_log2, float bias_exp,
                         int window, int keep_first, int H, int Hk, int S, int share_log2,
-                        const float* __restrict__ sinks, int gate_col, float cap_log2, float cap_arg) {
+                        const float* __restrict__ sinks, int gate_col, float cap_log2, float cap_arg, AbLayout lay) {
     extern __shared__ __align__(128) unsigned char ab_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
-    constexpr int KCHP = ab_pow2(KCH), VCHP = ab_pow2(VCH);   // a row's place in shared memory: chunks up to a power of two
+    constexpr int KCHP = ab_chunks(KCH), VCHP = ab_chunks(VCH);   // a row's place in shared memory
     constexpr int KROW = KCHP * 16, VROW = VCHP * 16;
     constexpr int K_BYTES = AB_BN * KROW, V_BYTES = AB_BN * VROW;
     constexpr int DVT = (DV + 31) / 32 * 4;   // output tiles of 8 columns, in fours (those past DV / 8 are computed on whatever
@@ -92,10 +107,10 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
     const int toks_per_tile = AB_BM >> share_log2;
     int row_base, n_new, off, seq;
     if (seg.cu_seqlens) {
-        row_base = seg.cu_seqlens[s];
-        n_new = seg.cu_seqlens[s + 1] - row_base;
-        off = seg.kv_offsets[s];
-        seq = s;
+        seq = seg.seq_list ? seg.seq_list[s] : s;
+        row_base = seg.cu_seqlens[seq];
+        n_new = seg.cu_seqlens[seq + 1] - row_base;
+        off = seg.kv_offsets[seq];
     } else {
         row_base = s;
         n_new = 1;
@@ -106,7 +121,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
     if (t0 >= n_new) return;
     const int hk = share > 1 ? blockIdx.y : blockIdx.y / (H / Hk);
     const int head0 = share > 1 ? hk * share : blockIdx.y;
-    const int* bt = block_table + (size_t)seq * max_blocks;
+    const int* bt = block_table + (size_t)(lay.table_by_segment ? s : seq) * max_blocks;
     const int toks_live = min(toks_per_tile, n_new - t0);
     const int kv_hi = off + t0 + toks_live;                              // one past the tile's last visible key
     const int kv_lo = window > 0 ? max(0, off + t0 + 1 - window) : 0;    // first key of the first row's window
@@ -141,7 +156,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
             key = min(key, kv_hi - 1);
             const int page = bt[key / S];
             cp_async16(ks + r * KROW + (ab_swz<KCHP>(r, cc) << 4),
-                       k_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DK + cc * 8);
+                       k_pool + (size_t)page * lay.k_page + (size_t)hk * lay.k_head + (size_t)(key % S) * lay.k_row + cc * 8);
         }
         for (int c = threadIdx.x; c < AB_BN * VCH; c += AB_WARPS * 32) {
             const int r = c / VCH, cc = c % VCH;
@@ -150,7 +165,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
             key = min(key, kv_hi - 1);
             const int page = bt[key / S];
             cp_async16(vs + r * VROW + (ab_swz<VCHP>(r, cc) << 4),
-                       v_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DV + cc * 8);
+                       v_pool + (size_t)page * lay.v_page + (size_t)hk * lay.v_head + (size_t)(key % S) * lay.v_row + cc * 8);
         }
     };
     issue(0, 0);
@@ -597,8 +612,8 @@ template <int DK, int DV>
 static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
                          int max_blocks, AbSegments seg, bf16* out, int out_row_stride, float scale, float bias_exp,
                          int window, int keep_first, int segments, int max_new, int H, int Hk, int S, const float* sinks,
-                         int gate_col, float softcap, cudaStream_t stream) {
-    constexpr int KROW = ab_pow2(DK / 8) * 16, VROW = ab_pow2(DV / 8) * 16;
+                         int gate_col, float softcap, const AbLayout* layout, cudaStream_t stream) {
+    constexpr int KROW = ab_chunks(DK / 8) * 16, VROW = ab_chunks(DV / 8) * 16;
     const size_t smem = (size_t)AB_BM * KROW + 2 * ((size_t)AB_BN * KROW + (size_t)AB_BN * VROW);
     static bool configured[VX_MAX_DEVICES];
     if (int rc = vx_configure_smem(biased_attention_kernel<DK, DV>, smem, configured)) return rc;
@@ -607,10 +622,12 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
     if (G > 1 && G <= 16 && (G & (G - 1)) == 0)
         while ((1 << share_log2) < G) ++share_log2;
     const int toks_per_tile = AB_BM >> share_log2;
+    AbLayout lay = {(long long)Hk * S * DK, (long long)S * DK, DK, (long long)Hk * S * DV, (long long)S * DV, DV, 0};
+    if (layout) lay = *layout;
     dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, share_log2 ? Hk : H, segments);
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_attention_kernel<DK, DV>), grid, AB_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
                 v_pool, block_table, max_blocks, seg, out, out_row_stride, scale * AB_LOG2E, bias_exp, window, keep_first, H,
-                Hk, S, share_log2, sinks, gate_col, softcap * AB_LOG2E, softcap > 0.f ? scale / softcap : 0.f);
+                Hk, S, share_log2, sinks, gate_col, softcap * AB_LOG2E, softcap > 0.f ? scale / softcap : 0.f, lay);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -619,20 +636,24 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
 // cu_seqlens null, seq_of_token and positions given, `segments` token rows (max_new = 1); with `runs` > 1 and a
 // float32 scratch of segments * H * runs * (DV + 2) elements a token's keys are cut into runs, a block each.
 // With softcap c > 0 a scaled score s becomes c tanh(s / c) before the bias by distance and the softmax.
-extern "C" int vx_biased_attention_cap(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
+static int biased_attention_any(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
                                        const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
                                        const int* seq_of_token, const int* positions, void* out, int out_row_stride,
                                        float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
                                        int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
-                                       int gate_col, float softcap, cudaStream_t stream) {
+                                       int gate_col, float softcap, const int* seq_list, const AbLayout* layout,
+                                       cudaStream_t stream) {
     if (segments <= 0 || max_new <= 0) return VX_OK;
     if (softcap < 0.f) return VX_ERR_SHAPE;
     if (H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
     if (cu_seqlens ? !kv_offsets : (!seq_of_token || !positions || max_new != 1)) return VX_ERR_SHAPE;
     if (H > 65535 || segments > 65535) return VX_ERR_LIMIT;
     if ((q_row_stride & 7) || (((uintptr_t)q) & 15) || (out_row_stride & 1) || (((uintptr_t)out) & 3)) return VX_ERR_ALIGN;
+    if (layout && (!cu_seqlens || ((layout->k_page | layout->k_head | layout->k_row | layout->v_page | layout->v_head | layout->v_row) & 7) ||
+                   (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15)))
+        return VX_ERR_ALIGN;
     if (!cu_seqlens) {
-        if (segments > 65535) return VX_ERR_LIMIT;
+        if (segments > 65535 || seq_list) return VX_ERR_LIMIT;
 #define AD_GO(K_, V_)                                                                                                       \
     if (DK == K_ && DV == V_)                                                                                               \
         return launch_biased_decode<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,       \
@@ -644,16 +665,43 @@ extern "C" int vx_biased_attention_cap(const void* q, int q_row_stride, const vo
 #undef AD_GO
         return VX_ERR_SHAPE;
     }
-    AbSegments seg = {cu_seqlens, kv_offsets, seq_of_token, positions};
+    AbSegments seg = {cu_seqlens, kv_offsets, seq_of_token, positions, seq_list};
 #define AB_GO(K_, V_)                                                                                                     \
     if (DK == K_ && DV == V_)                                                                                             \
         return launch_biased<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, \
                                      max_blocks, seg, (bf16*)out, out_row_stride, scale, bias_exp, window, keep_first,    \
-                                     segments, max_new, H, Hk, S, sinks, gate_col, softcap, stream)
+                                     segments, max_new, H, Hk, S, sinks, gate_col, softcap, layout, stream)
     AB_GO(64, 32); AB_GO(64, 64); AB_GO(64, 128); AB_GO(128, 32); AB_GO(128, 64); AB_GO(128, 128);
     AB_GO(32, 32); AB_GO(48, 48); AB_GO(80, 80); AB_GO(96, 96); AB_GO(112, 112);
+    AB_GO(192, 128); AB_GO(192, 64); AB_GO(96, 64); AB_GO(96, 32); AB_GO(256, 128);   // (portions only: no kernel for single tokens)
 #undef AB_GO
     return VX_ERR_SHAPE;
+}
+
+extern "C" int vx_biased_attention_cap(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
+                                       const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
+                                       const int* seq_of_token, const int* positions, void* out, int out_row_stride,
+                                       float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
+                                       int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
+                                       int gate_col, float softcap, cudaStream_t stream) {
+    return biased_attention_any(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, cu_seqlens, kv_offsets, seq_of_token,
+                                positions, out, out_row_stride, scale, bias_exp, window, keep_first, segments, max_new, H, Hk,
+                                DK, DV, S, scratch, runs, sinks, gate_col, softcap, nullptr, nullptr, stream);
+}
+
+// Portions whose keys and values lie as rows that a matrix product left: key j of head hk of segment s at
+// k + (table[s][j / S] * S + j % S) * k_row + hk * k_head (values alike); segment s is request seq_list[s] (null: s) in
+// cu_seqlens and kv_offsets.  Causal, no window, no bias by distance, no sink or gate.
+extern "C" int vx_biased_attention_rows(const void* q, int q_row_stride, const void* k, long long k_row, long long k_head,
+                                        const void* v, long long v_row, long long v_head, const int* block_table,
+                                        int max_blocks, const int* cu_seqlens, const int* kv_offsets, const int* seq_list,
+                                        void* out, int out_row_stride, float scale, int segments, int max_new, int H, int Hk,
+                                        int DK, int DV, int S, float softcap, cudaStream_t stream) {
+    AbLayout lay = {k_row * S, k_head, k_row, v_row * S, v_head, v_row, 1};
+    if (k_row < DK || v_row < DV) return VX_ERR_SHAPE;
+    return biased_attention_any(q, q_row_stride, k, v, block_table, max_blocks, cu_seqlens, kv_offsets, nullptr, nullptr, out,
+                                out_row_stride, scale, 0.f, 0, 0, segments, max_new, H, Hk, DK, DV, S, nullptr, 1, nullptr, -1,
+                                softcap, seq_list, &lay, stream);
 }
 
 extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,

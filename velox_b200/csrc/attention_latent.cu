@@ -170,3 +170,52 @@ extern "C" int vx_latent_attention(const void* qa, const void* pool, const int* 
                                              positions, (bf16*)out, scratch, scale, tokens, H, C, R, S, runs, stream);
     return VX_ERR_DTYPE;
 }
+
+// The cached rows of the segments of a step, gathered page by page into one matrix: segment s (request seq_list[s], or
+// s) holds positions 0 .. kv_offsets + new tokens - 1; its rows start at row table[s][0] * S_out of `rows` and are filled
+// with zeros up to the next multiple of S_out.  grid (run of 32 rows, segment); 8 warps, a warp per row.
+template <typename T>
+__global__ void latent_gather_kernel(const T* __restrict__ pool, const int* __restrict__ block_table, int max_blocks,
+                                     const int* __restrict__ cu_seqlens, const int* __restrict__ kv_offsets,
+                                     const int* __restrict__ seq_list, const int* __restrict__ out_table, int out_blocks,
+                                     T* __restrict__ rows, int W, int S, int S_out) {
+    pdl_wait();
+    pdl_trigger();
+    const int s = blockIdx.y, seq = seq_list ? seq_list[s] : s;
+    const int kv_len = kv_offsets[seq] + cu_seqlens[seq + 1] - cu_seqlens[seq];
+    const int padded = (kv_len + S_out - 1) / S_out * S_out;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* bt = block_table + (size_t)seq * max_blocks;
+    const size_t base = (size_t)out_table[(size_t)s * out_blocks] * S_out;
+    for (int j = blockIdx.x * 32 + warp; j < min(padded, blockIdx.x * 32 + 32); j += 8) {
+        T* dst = rows + (base + j) * W;
+        if (j < kv_len) {
+            const T* src = pool + ((size_t)bt[j / S] * S + (j % S)) * W;
+            for (int d = lane; d < W; d += 32) dst[d] = src[d];
+        } else {
+            for (int d = lane; d < W; d += 32) dst[d] = from_f32<T>(0.f);
+        }
+    }
+}
+
+// pool [pages, 1, S, W]; out_table int32 [segments, out_blocks]: the blocks of S_out rows that segment s takes in `rows`
+// (consecutive, the first one listed first); max_kv bounds any segment's positions after the step.
+extern "C" int vx_latent_gather(const void* pool, const int* block_table, int max_blocks, const int* cu_seqlens,
+                                const int* kv_offsets, const int* seq_list, const int* out_table, int out_blocks, void* rows,
+                                int segments, int max_kv, int W, int S, int S_out, int dtype, cudaStream_t stream) {
+    if (segments <= 0 || max_kv <= 0) return VX_OK;
+    if (W <= 0 || S <= 0 || S_out <= 0 || max_blocks <= 0 || out_blocks <= 0) return VX_ERR_SHAPE;
+    if (segments > 65535) return VX_ERR_LIMIT;
+    const int padded = (max_kv + S_out - 1) / S_out * S_out;
+    dim3 grid((padded + 31) / 32, segments);
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (latent_gather_kernel<float>), grid, 256, 0, stream, (const float*)pool, block_table,
+                    max_blocks, cu_seqlens, kv_offsets, seq_list, out_table, out_blocks, (float*)rows, W, S, S_out);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (latent_gather_kernel<bf16>), grid, 256, 0, stream, (const bf16*)pool, block_table,
+                    max_blocks, cu_seqlens, kv_offsets, seq_list, out_table, out_blocks, (bf16*)rows, W, S, S_out);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
+}

@@ -104,6 +104,9 @@ def _declare(lib) -> None:
         "vx_linear_attention_walk_parts": [P, I, I, I, I, P, P, I, F, P, I, I, P, F, F, P, P, P, P, I, I, I, I, I, I, P],
         "vx_stretch_log_decay": [P, I, F, P, P, I, I, P],
         "vx_stretch_scan": [P, P, P, P, P, P, P, I, I, I, I, P],
+        "vx_latent_gather": [P, P, I, P, P, P, P, I, P, I, I, I, I, I, I, P],
+        "vx_biased_attention_rows": [P, I, P, c_longlong, c_longlong, P, c_longlong, c_longlong, P, I, P, P, P, P, I, F, I, I, I, I, I,
+                                     I, I, F, P],
         "vx_head_norm_gate": [P, P, I, P, P, I, I, I, F, I, I, P],
         "vx_latent_prep": [P, I, P, I, P, P, F, P, I, P, P, P, I, I, I, I, I, I, P],
         "vx_capped_gated_act": [P, P, P, I, I, F, F, I, P],
@@ -978,14 +981,15 @@ def head_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.T
     return out
 
 
-def latent_prep(down: torch.Tensor, q: torch.Tensor, qa: torch.Tensor, weight: torch.Tensor, eps: float, inv_freq: torch.Tensor,
+def latent_prep(down: torch.Tensor, q: torch.Tensor, qa: Optional[torch.Tensor], weight: torch.Tensor, eps: float, inv_freq: torch.Tensor,
                 interleaved: bool, positions: torch.Tensor, slot_mapping, pool, heads: int, dim: int, rot_dim: int,
                 rank: int) -> None:
     """`down` [T, rank + rot_dim]: the first `rank` channels RMS-normed with `weight` and, followed by the rotated last
     `rot_dim`, written to `pool` (rows of rank + rot_dim elements) at the step's slots; the last rot_dim channels of every
-    head of `q` [T, heads * (dim + rot_dim)] rotated into the last rot_dim channels of `qa` [T, heads, rank + rot_dim]."""
+    head of `q` [T, heads * (dim + rot_dim)] rotated into the last rot_dim channels of `qa` [T, heads, rank + rot_dim], or,
+    with `qa` None, where they are."""
     _dev(down, q, qa, weight, inv_freq, positions, slot_mapping, pool)
-    _need(qa.is_contiguous() and qa.dtype == q.dtype and tuple(qa.shape) == (q.shape[0], heads, rank + rot_dim),
+    _need(qa is None or (qa.is_contiguous() and qa.dtype == q.dtype and tuple(qa.shape) == (q.shape[0], heads, rank + rot_dim)),
           "latent_prep: folded queries [T, heads, rank + rot_dim]")
     _need(down.stride(1) == 1 and q.stride(1) == 1 and down.dtype == q.dtype and positions.dtype == torch.int32,
           "latent_prep: rows contiguous, one element type, int32 positions")
@@ -1028,6 +1032,64 @@ def latent_attention(qa: torch.Tensor, pool: torch.Tensor, block_table: torch.Te
     _check(library().vx_latent_attention(_ptr(qa), _ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
                                          _ptr(positions), _ptr(out), _ptr(scratch), float(scale), tokens, heads, rank, rot_dim,
                                          pool.shape[2], runs, dtype_code(qa.dtype), _stream()), "latent_attention")
+    return out
+
+
+RAISED_ROWS_BLOCK = 64   # rows of keys and values raised for a step lie in blocks of this many, a request's in a row
+
+
+class RaisedPlan:
+    """Where the raised keys and values of a step's requests lie: request i (holding `kv_lens[i]` positions after the step)
+    takes the rows `first[i] * RAISED_ROWS_BLOCK` onward of a matrix of `rows` rows; `table` int32 [requests, blocks] lists
+    its blocks (on the device)."""
+
+    def __init__(self, kv_lens, device):
+        blocks = [-(-int(n) // RAISED_ROWS_BLOCK) for n in kv_lens]
+        self.max_blocks, self.first, at = max(blocks), [], 0
+        for b in blocks:
+            self.first.append(at)
+            at += b
+        self.rows, self.requests, self.max_kv = at * RAISED_ROWS_BLOCK, len(blocks), int(max(kv_lens))
+        table = [[f + min(j, b - 1) for j in range(self.max_blocks)] for f, b in zip(self.first, blocks)]
+        self.table = torch.tensor(table, dtype=torch.int32).to(device, non_blocking=True)
+
+
+def latent_gather(pool: torch.Tensor, block_table: torch.Tensor, cu_seqlens, kv_offsets, plan: RaisedPlan) -> torch.Tensor:
+    """The cached rows of every request of a step (positions 0 .. kv_offsets + new tokens - 1, new ones included) copied out
+    of their pages into one matrix [plan.rows, row width] where `plan` says; the rows up to the next block are zeros."""
+    _dev(pool, block_table, cu_seqlens, kv_offsets)
+    _need(pool.is_contiguous() and pool.dim() == 4 and pool.shape[1] == 1, "latent_gather: a pool [pages, 1, page size, width]")
+    _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.shape[0] >= plan.requests,
+          "latent_gather: int32 block table [requests, blocks]")
+    rows = torch.empty((plan.rows, pool.shape[3]), dtype=pool.dtype, device=pool.device)
+    _check(library().vx_latent_gather(_ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), None,
+                                      _ptr(plan.table), plan.max_blocks, _ptr(rows), plan.requests, plan.max_kv, pool.shape[3],
+                                      pool.shape[2], RAISED_ROWS_BLOCK, dtype_code(pool.dtype), _stream()), "latent_gather")
+    return rows
+
+
+RAISED_ATTENTION_SIZES = ((64, 32), (64, 64), (64, 128), (128, 32), (128, 64), (128, 128), (32, 32), (48, 48), (80, 80), (96, 96),
+                          (112, 112), (192, 128), (192, 64), (96, 64), (96, 32), (256, 128))
+
+
+def raised_attention_supported(dtype, key_dim: int, v_head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and (int(key_dim), int(v_head_dim)) in RAISED_ATTENTION_SIZES
+
+
+def raised_attention(q: torch.Tensor, q_row_stride: int, kv: torch.Tensor, cu_seqlens, kv_offsets, plan: RaisedPlan, scale: float,
+                     num_heads: int, key_dim: int, v_head_dim: int, max_new: int, softcap: float = 0.0) -> torch.Tensor:
+    """Causal attention of prompt portions over keys and values that a matrix product left as rows `kv`
+    [plan.rows, num_heads * (key_dim + v_head_dim)], a head's key followed by its value, request i's rows where `plan` says.
+    The tensor-core kernel of `biased_prefill_attention` with other strides.  Returns [tokens, num_heads * v_head_dim]."""
+    _dev(q, kv, cu_seqlens, kv_offsets)
+    per = key_dim + v_head_dim
+    _need(q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and kv.is_contiguous() and kv.shape[1] == num_heads * per,
+          "raised_attention: bfloat16 rows of heads * (key + value) elements")
+    out = torch.empty((q.shape[0], num_heads * v_head_dim), dtype=q.dtype, device=q.device)
+    _check(library().vx_biased_attention_rows(
+        _ptr(q), int(q_row_stride), _ptr(kv), kv.shape[1], per, kv.data_ptr() + 2 * key_dim, kv.shape[1], per, _ptr(plan.table),
+        plan.max_blocks, _ptr(cu_seqlens), _ptr(kv_offsets), None, _ptr(out), out.shape[1], float(scale), plan.requests,
+        int(max_new), num_heads, num_heads, key_dim, v_head_dim, RAISED_ROWS_BLOCK, float(softcap), _stream()), "raised_attention")
     return out
 
 

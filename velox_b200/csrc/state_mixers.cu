@@ -296,7 +296,7 @@ extern "C" int vx_head_norm_gate(const float* o, const void* g, int ldg, const f
 // head, D channels that stay and then R that are rotated the same way and written to the last R channels of the
 // head's row of qa [tokens, H, C + R] (whose first C channels another kernel fills).
 template <typename T>
-__global__ void latent_prep_kernel(const T* __restrict__ down, int ldd, const T* __restrict__ q, int ldq, T* __restrict__ qa,
+__global__ void latent_prep_kernel(const T* __restrict__ down, int ldd, T* q, int ldq, T* qa,
                                    const float* __restrict__ w, float eps, const float* __restrict__ inv_freq,
                                    int interleaved, const int* __restrict__ positions,
                                    const int* __restrict__ slot_mapping, T* __restrict__ pool, int H, int D, int R, int C) {
@@ -328,8 +328,8 @@ __global__ void latent_prep_kernel(const T* __restrict__ down, int ldd, const T*
         const int h = i / half, p = i - h * half;
         float sn, cs;
         sincosf(pos * inv_freq[p], &sn, &cs);
-        const T* qr = q + (size_t)t * ldq + (size_t)h * (D + R) + D;
-        T* qo = qa + ((size_t)t * H + h) * (C + R) + C;
+        T* qr = q + (size_t)t * ldq + (size_t)h * (D + R) + D;
+        T* qo = qa ? qa + ((size_t)t * H + h) * (C + R) + C : qr;   // (without folded queries: turned where they are)
         const int ia = interleaved ? 2 * p : p, ib = interleaved ? 2 * p + 1 : p + half;
         const float a = to_f32(qr[ia]), b = to_f32(qr[ib]);
         qo[ia] = from_f32<T>(a * cs - b * sn);
@@ -337,7 +337,7 @@ __global__ void latent_prep_kernel(const T* __restrict__ down, int ldd, const T*
     }
 }
 
-extern "C" int vx_latent_prep(const void* down, int ldd, const void* q, int ldq, void* qa, const float* w, float eps,
+extern "C" int vx_latent_prep(const void* down, int ldd, void* q, int ldq, void* qa, const float* w, float eps,
                               const float* inv_freq, int interleaved, const int* positions, const int* slot_mapping,
                               void* pool, int tokens, int H, int D, int R, int C, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
@@ -346,9 +346,9 @@ extern "C" int vx_latent_prep(const void* down, int ldd, const void* q, int ldq,
     if (slot_mapping && !pool) return VX_ERR_SHAPE;
     const int threads = C >= 512 ? 256 : 128;
     if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ROPE, (latent_prep_kernel<float>), tokens, threads, 0, stream, (const float*)down, ldd, (const float*)q, ldq, (float*)qa, w, eps, inv_freq, interleaved, positions, slot_mapping, (float*)pool, H, D, R, C);
+        VX_LAUNCH_K(VX_K_ROPE, (latent_prep_kernel<float>), tokens, threads, 0, stream, (const float*)down, ldd, (float*)q, ldq, (float*)qa, w, eps, inv_freq, interleaved, positions, slot_mapping, (float*)pool, H, D, R, C);
     else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ROPE, (latent_prep_kernel<bf16>), tokens, threads, 0, stream, (const bf16*)down, ldd, (const bf16*)q, ldq, (bf16*)qa, w, eps, inv_freq, interleaved, positions, slot_mapping, (bf16*)pool, H, D, R, C);
+        VX_LAUNCH_K(VX_K_ROPE, (latent_prep_kernel<bf16>), tokens, threads, 0, stream, (const bf16*)down, ldd, (bf16*)q, ldq, (bf16*)qa, w, eps, inv_freq, interleaved, positions, slot_mapping, (bf16*)pool, H, D, R, C);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();

@@ -11,6 +11,10 @@ never formed: since q_h . (W_uk,h c) = (W_uk,h^T q_h) . c, a step folds W_uk int
 head), attends over the cached rows as ONE key/value head of width kv_rank + rot_dim whose value is the row's first
 kv_rank elements (`ops.latent_attention`: a tile of rows is staged once for eight heads), and raises the attended latent
 vector through W_uv afterwards (again one product per head).
+A step that brings a prompt portion of `RAISE_MIN_TOKENS` tokens or more (bfloat16, key and value sizes the tensor-core
+kernel takes) goes the other way round: the cached rows of its requests are copied out of their pages into one matrix, ONE
+product with [W_uk,h 0; 0 I; W_uv,h 0] per head leaves every head's key [W_uk,h c ; r] and value side by side, and the
+tensor-core prompt kernel (`ops.raised_attention`) reads them there with the queries as the projection left them.
 Angles, the latent norm, scores and the softmax are float32.  The rotation takes either layout of the position part.
 """
 from __future__ import annotations
@@ -24,6 +28,10 @@ from .base import Mixer, PagedLatent, Runtime, TensorSpec
 from .linear import Linear
 from .plan import PartSpec
 from .registry import build_part
+
+
+RAISE_MIN_TOKENS = 16        # longest portion of a step from which keys and values are raised for the tensor-core kernel
+RAISE_MAX_BYTES = 2 << 30    # the most that the raised keys and values of a step may take
 
 
 class LatentAttention(Mixer):
@@ -50,7 +58,7 @@ class LatentAttention(Mixer):
         self.names = dict(zip(("q", "dkv", "norm", "uk", "uv", "o"), (prefix + n for n in names)))
         self.proj: Optional[Linear] = None
         self.out: Optional[Linear] = None
-        self.norm_weight = self.uk_t = self.uv = self.rotary = None
+        self.norm_weight = self.uk_t = self.uv = self.rotary = self.raise_w = None
 
     @property
     def row(self) -> int:
@@ -73,6 +81,14 @@ class LatentAttention(Mixer):
         self.uk_t = tensors[n["uk"]].view(H, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
         self.uv = tensors[n["uv"]].view(H, self.v_head_dim, self.kv_rank).contiguous()
         self.out = Linear(tensors[n["o"]])
+        D, R, C, Dv = self.head_dim, self.rot_dim, self.kv_rank, self.v_head_dim
+        if ops.raised_attention_supported(tensors[n["uk"]].dtype, D + R, Dv):
+            # per head: D rows [W_uk,h | 0], R rows [0 | I] (the shared rotated part), Dv rows [W_uv,h | 0]
+            w = torch.zeros((H, D + R + Dv, C + R), dtype=tensors[n["uk"]].dtype, device=tensors[n["uk"]].device)
+            w[:, :D, :C] = tensors[n["uk"]].view(H, D, C)
+            w[:, D:D + R, C:] = torch.eye(R, dtype=w.dtype, device=w.device)
+            w[:, D + R:, :C] = tensors[n["uv"]].view(H, Dv, C)
+            self.raise_w = Linear(w.view(H * (D + R + Dv), C + R))
         self.position.bind(tensors, runtime)
         self.rotary = self.position.rotary_table(runtime.device)
 
@@ -85,8 +101,19 @@ class LatentAttention(Mixer):
         group = ctx.groups[cache.group]
         x = self.proj(h)                       # [tokens, H (D + R) | C + R]
         q, down = x[:, :H * (D + R)], x[:, H * (D + R):]
+        interleaved = bool(getattr(self.position, "interleaved", False))
+        if (self.raise_w is not None and ctx.max_new >= RAISE_MIN_TOKENS and len(ctx.new_lens) == ctx.n_seqs
+                and len(ctx.offsets) == ctx.n_seqs):
+            plan = ops.RaisedPlan([a + b for a, b in zip(ctx.offsets, ctx.new_lens)], x.device)
+            if plan.rows * H * (D + R + Dv) * 2 <= RAISE_MAX_BYTES:
+                ops.latent_prep(down, q, None, self.norm_weight, self.eps, self.rotary[0], interleaved, ctx.positions,
+                                group.slot_mapping if cache.writes else None, cache.pages, H, D, R, C)
+                kv = self.raise_w(ops.latent_gather(cache.pages, group.block_table, ctx.cu_seqlens, ctx.kv_offsets, plan))
+                o = ops.raised_attention(x, x.shape[1], kv, ctx.cu_seqlens, ctx.kv_offsets, plan, self.scale, H, D + R, Dv,
+                                         ctx.max_new)
+                return self.out(o)
         qa = torch.empty((t, H, C + R), dtype=x.dtype, device=x.device)   # folded queries: [W_uk^T q | rotated part]
-        ops.latent_prep(down, q, qa, self.norm_weight, self.eps, self.rotary[0], bool(getattr(self.position, "interleaved", False)),
+        ops.latent_prep(down, q, qa, self.norm_weight, self.eps, self.rotary[0], interleaved,
                         ctx.positions, group.slot_mapping if cache.writes else None, cache.pages, H, D, R, C)
         ops.gemm_heads(q.view(t, H, D + R)[:, :, :D], self.uk_t, qa[:, :, :C])
         latent = ops.latent_attention(qa, cache.pages, group.block_table, ctx.seq_of_token, ctx.positions, self.scale, H, C, R,
