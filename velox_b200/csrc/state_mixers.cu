@@ -15,69 +15,83 @@
 // the activations that feed matrix products.
 #include "common.cuh"
 
-#define LW_COLS 32
-#define LW_SLICES 4
-#define LW_CHUNK 16
-#define LW_MAX_SMEM (sizeof(float) * LW_CHUNK * (3 * 256 + LW_COLS))   // D up to 256, with a gate
+#define LW_COLS 32      // state columns of a block
+#define LW_CC 4         // ... of a thread
+#define LW_GROUPS 16    // row groups: 4 in a warp (lane bits 3, 4) times 4 warps
+#define LW_CHUNK 16     // tokens staged at a time
+#define LW_THREADS 128
+// q, k and, with a gate, the decays of a chunk (rows padded to 16 R, R <= 16), v, the warps' partial outputs
+#define LW_SMEM(DP, GATED) (sizeof(float) * LW_CHUNK * (((GATED) ? 3 : 2) * (DP) + LW_COLS + 4 * LW_COLS))
+#define LW_MAX_SMEM LW_SMEM(256, 1)
 
 __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - log1pf(expf(-fabsf(z))); }
 
-// A block owns LW_COLS columns of one head's state of one request; a thread owns every fourth row of
-// one column.  Tokens are staged LW_CHUNK at a time in shared memory, in float32: q and k as the
-// projection left them, turned by position * inv_freq[i] on the first rot_dim channels (pairs
-// (i, i + rot_dim/2), or (2i, 2i + 1) when `interleaved`), then times q_mul / k_mul.  The decay of
-// channel d at token t is decay[h] (`gate` null), or exp(gate_mul * log_sigmoid(gate[t, h D + d])):
-// sigmoid(z)^(gate_mul), formed through the logarithm.  Every sum runs in an order fixed by D alone.
-template <typename T, int DR>
-__global__ void __launch_bounds__(LW_COLS * LW_SLICES)
+// A block owns LW_COLS columns of one head's state of one request; a thread owns a tile of R consecutive rows by 4
+// consecutive columns (rows [g R, g R + R) for its row group g = 4 warp + (lane >> 3), columns 4 (lane & 7) ..), so a
+// token costs it 2 (3 with a gate) R / 4 + 1 reads of 16 bytes from shared memory for 3 R 4 multiply-adds.  Tokens are
+// staged LW_CHUNK at a time in shared memory, in float32, rows padded to 16 R with q = k = 0: q and k as the projection left
+// them, turned by position * inv_freq[i] on the first rot_dim channels (pairs (i, i + rot_dim/2), or (2i, 2i + 1) when
+// `interleaved`), then times q_mul / k_mul.  The decay of channel d at token t is decay[h] (`gate` null), or
+// exp(gate_mul * log_sigmoid(gate[t, h D + d])): sigmoid(z)^(gate_mul), formed through the logarithm.  A token's output
+// column is summed over a thread's rows in order, then over the 4 row groups of a warp by two exchanges, then over the warps
+// in warp order (through shared memory, once a chunk): an order fixed by D alone.
+template <typename T, int R, bool GATED>
+__global__ void __launch_bounds__(LW_THREADS, 4)
 linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_col, int v_col,
                              const float* __restrict__ decay, const float* __restrict__ gate, int ldg, float gate_mul,
                              const float* __restrict__ inv_freq, int rot_dim, int interleaved,
                              const int* __restrict__ positions, float q_mul, float k_mul, float* __restrict__ state,
                              const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots,
                              float* __restrict__ out, int H, int D, int Dv, int fresh) {
-    extern __shared__ float smem[];
-    float* q_s = smem;                       // [LW_CHUNK][D]
-    float* k_s = q_s + LW_CHUNK * D;         // [LW_CHUNK][D]
-    float* v_s = k_s + LW_CHUNK * D;         // [LW_CHUNK][LW_COLS]
-    float* a_s = v_s + LW_CHUNK * LW_COLS;   // [LW_CHUNK][D] (with a gate only)
+    extern __shared__ __align__(16) float smem[];
+    constexpr int DP = LW_GROUPS * R;
+    float* q_s = smem;                            // [LW_CHUNK][DP]
+    float* k_s = q_s + LW_CHUNK * DP;             // [LW_CHUNK][DP]
+    float* v_s = k_s + LW_CHUNK * DP;             // [LW_CHUNK][LW_COLS]
+    float* o_s = v_s + LW_CHUNK * LW_COLS;        // [4 warps][LW_CHUNK][LW_COLS]
+    float* a_s = o_s + 4 * LW_CHUNK * LW_COLS;    // [LW_CHUNK][DP] (with a gate only)
     const int col0 = blockIdx.x * LW_COLS, h = blockIdx.y, seq = blockIdx.z;
-    const int col = threadIdx.x / LW_SLICES, slice = threadIdx.x % LW_SLICES;
-    const int c = col0 + col;
-    const bool live = c < Dv;
-    const float dec = decay ? decay[h] : 1.f;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int cg = lane & 7, row0 = (warp * 4 + (lane >> 3)) * R, c0 = col0 + cg * LW_CC;
+    const float dec = GATED ? 1.f : decay[h];
     const int half = rot_dim >> 1;
     pdl_wait();
     pdl_trigger();
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
     float* st = state + (((size_t)state_slots[seq] * H + h) * D) * Dv;
-    float S[DR];
+    float S[R][LW_CC];
 #pragma unroll
-    for (int i = 0; i < DR; ++i) {
-        const int d = slice + LW_SLICES * i;
-        S[i] = (live && d < D && !fresh) ? st[(size_t)d * Dv + c] : 0.f;
-    }
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < LW_CC; ++c)
+            S[r][c] = (!fresh && row0 + r < D && c0 + c < Dv) ? st[(size_t)(row0 + r) * Dv + c0 + c] : 0.f;
     for (int tb = t0; tb < t1; tb += LW_CHUNK) {
         const int n = min(LW_CHUNK, t1 - tb);
         __syncthreads();
-        for (int i = threadIdx.x; i < n * D; i += blockDim.x) {
-            const int tt = i / D, d = i - tt * D;
-            const T* row = x + (size_t)(tb + tt) * ldx + (size_t)h * D + d;
-            q_s[i] = to_f32(row[q_col]);
-            k_s[i] = to_f32(row[k_col]);
-            if (gate) a_s[i] = expf(gate_mul * log_sigmoid(gate[(size_t)(tb + tt) * ldg + (size_t)h * D + d]));
+        for (int i = threadIdx.x; i < n * DP; i += LW_THREADS) {
+            const int tt = i / DP, d = i - tt * DP;
+            float qv = 0.f, kv = 0.f, av = 1.f;
+            if (d < D) {
+                const T* row = x + (size_t)(tb + tt) * ldx + (size_t)h * D + d;
+                qv = to_f32(row[q_col]);
+                kv = to_f32(row[k_col]);
+                if (GATED) av = expf(gate_mul * log_sigmoid(gate[(size_t)(tb + tt) * ldg + (size_t)h * D + d]));
+            }
+            q_s[i] = qv;
+            k_s[i] = kv;
+            if (GATED) a_s[i] = av;
         }
-        for (int i = threadIdx.x; i < n * LW_COLS; i += blockDim.x) {
+        for (int i = threadIdx.x; i < n * LW_COLS; i += LW_THREADS) {
             const int tt = i / LW_COLS, cc = i - tt * LW_COLS;
             v_s[i] = (col0 + cc < Dv) ? to_f32(x[(size_t)(tb + tt) * ldx + v_col + (size_t)h * Dv + col0 + cc]) : 0.f;
         }
         __syncthreads();
         if (inv_freq && half > 0) {
-            for (int i = threadIdx.x; i < n * half; i += blockDim.x) {
+            for (int i = threadIdx.x; i < n * half; i += LW_THREADS) {
                 const int tt = i / half, p = i - tt * half;
                 float sn, cs;
                 sincosf((float)positions[tb + tt] * inv_freq[p], &sn, &cs);
-                const int ia = tt * D + (interleaved ? 2 * p : p), ib = tt * D + (interleaved ? 2 * p + 1 : p + half);
+                const int ia = tt * DP + (interleaved ? 2 * p : p), ib = tt * DP + (interleaved ? 2 * p + 1 : p + half);
                 const float qa = q_s[ia], qb = q_s[ib], ka = k_s[ia], kb = k_s[ib];
                 q_s[ia] = qa * cs - qb * sn;
                 q_s[ib] = qb * cs + qa * sn;
@@ -87,33 +101,54 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
             __syncthreads();
         }
         if (q_mul != 1.f || k_mul != 1.f) {
-            for (int i = threadIdx.x; i < n * D; i += blockDim.x) { q_s[i] *= q_mul; k_s[i] *= k_mul; }
+            for (int i = threadIdx.x; i < n * DP; i += LW_THREADS) { q_s[i] *= q_mul; k_s[i] *= k_mul; }
             __syncthreads();
         }
         for (int tt = 0; tt < n; ++tt) {
-            const float v = v_s[tt * LW_COLS + col];
-            const float* kq = k_s + tt * D;
-            const float* qq = q_s + tt * D;
-            const float* aa = a_s + tt * D;
-            float o = 0.f;
+            const float4 v4 = *reinterpret_cast<const float4*>(v_s + tt * LW_COLS + cg * LW_CC);
+            const float v[LW_CC] = {v4.x, v4.y, v4.z, v4.w};
+            float o[LW_CC] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int i = 0; i < DR; ++i) {
-                const int d = slice + LW_SLICES * i;
-                if (d < D) {
-                    S[i] = fmaf(gate ? aa[d] : dec, S[i], kq[d] * v);
-                    o = fmaf(S[i], qq[d], o);
-                }
+            for (int r4 = 0; r4 < R; r4 += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(k_s + tt * DP + row0 + r4);
+                const float4 q4 = *reinterpret_cast<const float4*>(q_s + tt * DP + row0 + r4);
+                float4 a4 = make_float4(dec, dec, dec, dec);
+                if (GATED) a4 = *reinterpret_cast<const float4*>(a_s + tt * DP + row0 + r4);
+                const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w}, aa[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int c = 0; c < LW_CC; ++c) {
+                        S[r4 + r][c] = fmaf(aa[r], S[r4 + r][c], kk[r] * v[c]);
+                        o[c] = fmaf(S[r4 + r][c], qq[r], o[c]);
+                    }
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (slice == 0 && live && out) out[(size_t)(tb + tt) * H * Dv + (size_t)h * Dv + c] = o;
+            if (out) {
+                // over the warp's 4 row groups: the upper pair keeps columns 2, 3 and the lower pair 0, 1, then odd groups keep
+                // the second of their two; lane (g, cg) ends with column 4 cg + 2 (g >> 1) + (g & 1)
+                const bool hi = lane & 16, mid = lane & 8;
+                const float r0 = __shfl_xor_sync(0xffffffffu, hi ? o[0] : o[2], 16);
+                const float r1 = __shfl_xor_sync(0xffffffffu, hi ? o[1] : o[3], 16);
+                const float a0 = (hi ? o[2] : o[0]) + r0, a1 = (hi ? o[3] : o[1]) + r1;
+                const float r2 = __shfl_xor_sync(0xffffffffu, mid ? a0 : a1, 8);
+                o_s[(warp * LW_CHUNK + tt) * LW_COLS + cg * LW_CC + (hi ? 2 : 0) + (mid ? 1 : 0)] = (mid ? a1 : a0) + r2;
+            }
+        }
+        if (out) {
+            __syncthreads();
+            for (int i = threadIdx.x; i < n * LW_COLS; i += LW_THREADS) {
+                const int tt = i / LW_COLS, cc = i - tt * LW_COLS;
+                if (col0 + cc < Dv)
+                    out[(size_t)(tb + tt) * H * Dv + (size_t)h * Dv + col0 + cc] =
+                        ((o_s[i] + o_s[LW_CHUNK * LW_COLS + i]) + o_s[2 * LW_CHUNK * LW_COLS + i]) + o_s[3 * LW_CHUNK * LW_COLS + i];
+            }
         }
     }
 #pragma unroll
-    for (int i = 0; i < DR; ++i) {
-        const int d = slice + LW_SLICES * i;
-        if (live && d < D) st[(size_t)d * Dv + c] = S[i];
-    }
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < LW_CC; ++c)
+            if (row0 + r < D && c0 + c < Dv) st[(size_t)(row0 + r) * Dv + c0 + c] = S[r][c];
 }
 
 template <typename T>
@@ -123,20 +158,23 @@ static int launch_linear_attention_walk(const T* x, int ldx, int q_col, int k_co
                                         const int* cu_seqlens, const int* state_slots, float* out, int seqs, int H, int D,
                                         int Dv, int fresh, cudaStream_t stream) {
     dim3 grid((Dv + LW_COLS - 1) / LW_COLS, H, seqs);
-    const size_t smem = sizeof(float) * LW_CHUNK * ((gate ? 3 : 2) * D + LW_COLS);
-    const int dr = (D + LW_SLICES - 1) / LW_SLICES;
-    static bool configured[4][VX_MAX_DEVICES];
-#define LW_GO(DR, SLOT)                                                                                                \
-    do {                                                                                                               \
-        if (int rc = vx_configure_smem(linear_attention_walk_kernel<T, DR>, LW_MAX_SMEM, configured[SLOT])) return rc;          \
-        VX_LAUNCH_K(VX_K_ATTENTION, (linear_attention_walk_kernel<T, DR>), grid, LW_COLS * LW_SLICES, smem, stream, x,  \
-                    ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul, inv_freq, rot_dim, interleaved, positions,    \
-                    q_mul, k_mul, state, cu_seqlens, state_slots, out, H, D, Dv, fresh);                                \
+    static bool configured[8][VX_MAX_DEVICES];
+#define LW_GO(R_, G_, SLOT)                                                                                                \
+    do {                                                                                                                   \
+        if (int rc = vx_configure_smem(linear_attention_walk_kernel<T, R_, G_>, LW_MAX_SMEM, configured[SLOT])) return rc; \
+        VX_LAUNCH_K(VX_K_ATTENTION, (linear_attention_walk_kernel<T, R_, G_>), grid, LW_THREADS, LW_SMEM(LW_GROUPS * R_, G_), \
+                    stream, x, ldx, q_col, k_col, v_col, decay, gate, ldg, gate_mul, inv_freq, rot_dim, interleaved,       \
+                    positions, q_mul, k_mul, state, cu_seqlens, state_slots, out, H, D, Dv, fresh);                        \
     } while (0)
-    if (dr <= 8) LW_GO(8, 0);
-    else if (dr <= 16) LW_GO(16, 1);
-    else if (dr <= 32) LW_GO(32, 2);
-    else LW_GO(64, 3);
+#define LW_GO_R(R_, SLOT)                                                                                                  \
+    do {                                                                                                                   \
+        if (gate) LW_GO(R_, true, 2 * SLOT); else LW_GO(R_, false, 2 * SLOT + 1);                                          \
+    } while (0)
+    if (D <= 64) LW_GO_R(4, 0);
+    else if (D <= 128) LW_GO_R(8, 1);
+    else if (D <= 192) LW_GO_R(12, 2);
+    else LW_GO_R(16, 3);
+#undef LW_GO_R
 #undef LW_GO
     VX_LAUNCH_CHECK();
     return VX_OK;
@@ -210,12 +248,22 @@ __global__ void stretch_scan_kernel(float* __restrict__ parts, float* __restrict
     float* st = state + (size_t)state_slots[seq] * per + e;
     float S = *st;
     const float l2 = decay ? log2f(decay[h]) : 0.f;
-    for (int c = first_stretch[seq]; c < first_stretch[seq + 1]; ++c) {
-        float* p = parts + (size_t)c * per + e;
-        const float loc = *p;
-        *p = S;
-        const float a = log_a ? expf(log_a[(size_t)c * H * D + hd]) : exp2f((float)(cu_stretch[c + 1] - cu_stretch[c]) * l2);
-        S = fmaf(a, S, loc);
+    const int last = first_stretch[seq + 1];
+    for (int c = first_stretch[seq]; c < last; c += 4) {   // (four stretches' reads in flight before the first write)
+        float loc[4], a[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (c + u >= last) continue;
+            loc[u] = parts[(size_t)(c + u) * per + e];
+            a[u] = log_a ? expf(log_a[(size_t)(c + u) * H * D + hd])
+                         : exp2f((float)(cu_stretch[c + u + 1] - cu_stretch[c + u]) * l2);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (c + u >= last) continue;
+            parts[(size_t)(c + u) * per + e] = S;
+            S = fmaf(a[u], S, loc[u]);
+        }
     }
     *st = S;
 }
