@@ -124,7 +124,8 @@ def test_one_key_that_would_dominate_is_held_by_the_bound_wherever_it_lies(dtype
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,D,R,Dv,C,interleaved", [(3, 12, 6, 10, 20, True), (4, 32, 64, 32, 64, True), (2, 16, 8, 16, 24, False),
-                                                    (11, 8, 4, 8, 33, True), (2, 16, 32, 16, 300, True), (1, 8, 2, 8, 520, False)])
+                                                    (19, 8, 4, 8, 33, True), (2, 16, 32, 16, 300, True), (1, 8, 2, 8, 520, False),
+                                                    (5, 16, 8, 16, 136, True)])
 def test_latent_rows_are_prepared_cached_and_attended_as_the_plain_mixer_does(dtype, H, D, R, Dv, C, interleaved):
     """The mixer's middle (everything between its input projection and its output projection) on projected rows: the latent
     norm and the rotations into the page, the queries folded through W_uk, attention over rows whose value is the start of

@@ -2,33 +2,61 @@
 // rotated channels that all heads share), and a query head brings a folded query of the same width, so that
 //   score(i, j) = qa_i . row_j * scale,   causal softmax,   out_i = sum_j w_ij row_j[0 .. C)
 // (the value is the first C elements of the key's row).  All heads of a token read the same rows, so a block stages
-// a tile of rows once for up to eight heads.
+// a tile of rows once for up to sixteen heads.
 //
-// One block per (token row, group of 8 heads, run of keys); a warp per head.  A tile of 32 rows is copied into shared
-// memory as float32, each row on an odd stride, so that lane j forms the whole product qa . row_j without bank
-// conflicts (the folded queries lie beside the tile, read as broadcasts); the warp keeps a running maximum, sum and
-// accumulator (lane l owns value channels l, l + 32, ...) and adds the 32 rows in key order.  With `runs` > 1 a token's
-// tiles are dealt to the runs in contiguous stretches, every run writes (maximum, sum, accumulator) to a scratch
-// buffer, and a join kernel adds them in run order.  Scores, weights and sums are float32; the order of every sum
-// depends on the token's own position and on `runs` alone.
+// One block per (token row, group of 16 heads, run of keys); a warp per 4 heads.  A tile of 32 rows is copied into shared
+// memory as float32, each row on a stride of 4 (mod 32) elements, so that lane j reads row j sixteen bytes at a time without
+// bank conflicts; the folded queries lie beside the tile and are read as broadcasts.  A lane forms the products of row j with
+// its warp's 4 queries (every element of the row read once for the four), the warp keeps a running maximum, sum and
+// accumulator per head (lane l owns value channels 4 (l + 32 i) .. + 3) and adds the 32 rows in key order, every element of a
+// row again read once for the four heads.  With `runs` > 1 a token's tiles are dealt to the runs in contiguous stretches,
+// every run writes (maximum, sum, accumulator) to a scratch buffer, and a join kernel adds them in run order.  Scores,
+// weights and sums are float32; the order of every sum depends on the token's own position and on `runs` alone.
 #include "common.cuh"
 
-#define AL_WARPS 8
+#define AL_WARPS 4
+#define AL_HW 4                       // heads of a warp
+#define AL_HEADS (AL_WARPS * AL_HW)   // heads of a block
 #define AL_TILE 32
 
-template <typename T, int NR>
+__host__ __device__ inline int al_row_stride(int W) {   // the least number >= W that is 4 mod 32
+    const int w4 = (W + 3) & ~3;
+    return w4 + ((4 - w4) & 31);
+}
+
+template <typename T>
+__device__ __forceinline__ void al_stage_row(float* dst, const T* src, int W, int Wp, int lane) {
+    for (int d = lane; d < Wp; d += 32) dst[d] = d < W ? to_f32(src[d]) : 0.f;
+}
+template <>
+__device__ __forceinline__ void al_stage_row<bf16>(float* dst, const bf16* src, int W, int Wp, int lane) {
+    if ((W & 7) == 0 && (((uintptr_t)src) & 15) == 0) {   // eight elements a load
+        for (int d = lane * 8; d < W; d += 256) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + d);
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+            const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
+            const float2 c = __bfloat1622float2(h2[2]), e = __bfloat1622float2(h2[3]);
+            *reinterpret_cast<float4*>(dst + d) = make_float4(a.x, a.y, b.x, b.y);
+            *reinterpret_cast<float4*>(dst + d + 4) = make_float4(c.x, c.y, e.x, e.y);
+        }
+        return;
+    }
+    for (int d = lane; d < Wp; d += 32) dst[d] = d < W ? __bfloat162float(src[d]) : 0.f;
+}
+
+template <typename T, int NR4>
 __global__ void __launch_bounds__(AL_WARPS * 32)
 latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, const int* __restrict__ block_table,
                         int max_blocks, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                         T* __restrict__ out, float* __restrict__ scratch, float scale, int H, int C, int R, int S, int runs) {
-    extern __shared__ float al_smem[];
-    const int W = C + R, ld = W | 1;
+    extern __shared__ __align__(16) float al_smem[];
+    const int W = C + R, Wp = (W + 3) & ~3, ld = al_row_stride(W);
     float* k_s = al_smem;                    // [AL_TILE][ld]
-    float* q_s = k_s + AL_TILE * ld;         // [AL_WARPS][W]
-    const int t = blockIdx.x, h0 = blockIdx.y * AL_WARPS, run = blockIdx.z;
+    float* q_s = k_s + AL_TILE * ld;         // [AL_HEADS][Wp]
+    float* p_s = q_s + AL_HEADS * Wp;        // [AL_WARPS][AL_TILE][AL_HW]
+    const int t = blockIdx.x, h0 = blockIdx.y * AL_HEADS, run = blockIdx.z;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int h = h0 + warp;
-    const bool live = h < H;
+    const int hw0 = h0 + warp * AL_HW;       // the warp's first head
     pdl_wait();
     pdl_trigger();
     const int kv_len = positions[t] + 1;
@@ -37,92 +65,150 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
     const int per_run = (tiles + runs - 1) / runs;
     const int tile0 = run * per_run, tile1 = min(tiles, tile0 + per_run);
 
-    const int heads_here = min(AL_WARPS, H - h0);
-    for (int i = threadIdx.x; i < heads_here * W; i += blockDim.x)
-        q_s[i] = to_f32(qa[((size_t)t * H + h0) * W + i]);
+    for (int hh = warp; hh < AL_HEADS; hh += AL_WARPS) {
+        float* dst = q_s + hh * Wp;
+        if (h0 + hh < H) {
+            al_stage_row<T>(dst, qa + ((size_t)t * H + h0 + hh) * W, W, Wp, lane);
+        } else {
+            for (int d = lane; d < Wp; d += 32) dst[d] = 0.f;
+        }
+    }
 
-    float acc[NR];
+    float acc[AL_HW][NR4][4];
 #pragma unroll
-    for (int i = 0; i < NR; ++i) acc[i] = 0.f;
-    float m = -INFINITY, l = 0.f;
-    const float* qh = q_s + warp * W;
+    for (int hh = 0; hh < AL_HW; ++hh)
+#pragma unroll
+        for (int i = 0; i < NR4; ++i) acc[hh][i][0] = acc[hh][i][1] = acc[hh][i][2] = acc[hh][i][3] = 0.f;
+    float m[AL_HW], l[AL_HW];
+#pragma unroll
+    for (int hh = 0; hh < AL_HW; ++hh) { m[hh] = -INFINITY; l[hh] = 0.f; }
+    const float* qw = q_s + warp * AL_HW * Wp;
+    float* pw = p_s + warp * AL_TILE * AL_HW;
 
     for (int tile = tile0; tile < tile1; ++tile) {
         const int j0 = tile * AL_TILE, n = min(AL_TILE, kv_len - j0);
         __syncthreads();   // the tile before this one has been used (and, the first time, the queries are written)
-        for (int r = warp; r < n; r += AL_WARPS) {
-            const int j = j0 + r;
-            const T* src = pool + ((size_t)bt[j / S] * S + (j % S)) * W;
+        const int my_page = lane < n ? bt[(j0 + lane) / S] : 0;   // (one trip to the table for the tile's 32 rows)
+#pragma unroll
+        for (int r8 = 0; r8 < AL_TILE / AL_WARPS; ++r8) {
+            const int r = warp + r8 * AL_WARPS;
+            const int page = __shfl_sync(0xffffffffu, my_page, r);
             float* dst = k_s + r * ld;
-            for (int d = lane; d < W; d += 32) dst[d] = to_f32(src[d]);
-        }
-        __syncthreads();
-        if (!live) continue;
-        float s = -INFINITY;
-        if (lane < n) {
-            const float* kr = k_s + lane * ld;
-            float dot = 0.f;
-            for (int d = 0; d < W; ++d) dot = fmaf(qh[d], kr[d], dot);
-            s = dot * scale;
-        }
-        const float m_new = fmaxf(m, warp_max(s));
-        const float p = lane < n ? expf(s - m_new) : 0.f;
-        const float alpha = expf(m - m_new);   // m = -inf before the first tile: 0
-        l = l * alpha + warp_sum(p);
-#pragma unroll
-        for (int i = 0; i < NR; ++i) acc[i] *= alpha;
-        for (int jj = 0; jj < n; ++jj) {
-            const float pj = __shfl_sync(0xffffffffu, p, jj);
-            const float* vr = k_s + jj * ld;
-#pragma unroll
-            for (int i = 0; i < NR; ++i) {
-                const int d = lane + 32 * i;
-                if (d < C) acc[i] = fmaf(pj, vr[d], acc[i]);
+            if (r < n) {
+                al_stage_row<T>(dst, pool + ((size_t)page * S + ((j0 + r) % S)) * W, W, Wp, lane);
+            } else {
+                for (int d = lane; d < Wp; d += 32) dst[d] = 0.f;
             }
         }
-        m = m_new;
-    }
-    if (!live) return;
-    if (runs == 1) {
-        const float inv = 1.f / l;   // (a token always sees itself: l > 0)
-        T* dst = out + ((size_t)t * H + h) * C;
+        __syncthreads();
+        if (hw0 >= H) continue;
+        float dot[AL_HW] = {0.f, 0.f, 0.f, 0.f};
+        const float* kr = k_s + lane * ld;
+        for (int d = 0; d < Wp; d += 4) {
+            const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
-        for (int i = 0; i < NR; ++i) {
-            const int d = lane + 32 * i;
-            if (d < C) dst[d] = from_f32<T>(acc[i] * inv);
+            for (int hh = 0; hh < AL_HW; ++hh) {
+                const float4 q4 = *reinterpret_cast<const float4*>(qw + hh * Wp + d);
+                dot[hh] = fmaf(q4.x, k4.x, dot[hh]);
+                dot[hh] = fmaf(q4.y, k4.y, dot[hh]);
+                dot[hh] = fmaf(q4.z, k4.z, dot[hh]);
+                dot[hh] = fmaf(q4.w, k4.w, dot[hh]);
+            }
         }
-        return;
-    }
-    float* dst = scratch + (((size_t)t * H + h) * runs + run) * (C + 2);
-    if (lane == 0) { dst[0] = m; dst[1] = l; }
+        float p[AL_HW];
 #pragma unroll
-    for (int i = 0; i < NR; ++i) {
-        const int d = lane + 32 * i;
-        if (d < C) dst[2 + d] = acc[i];
+        for (int hh = 0; hh < AL_HW; ++hh) {
+            const float s = lane < n ? dot[hh] * scale : -INFINITY;
+            const float m_new = fmaxf(m[hh], warp_max(s));
+            p[hh] = lane < n ? expf(s - m_new) : 0.f;
+            const float alpha = expf(m[hh] - m_new);   // m = -inf before the first tile: 0
+            l[hh] = l[hh] * alpha + warp_sum(p[hh]);
+#pragma unroll
+            for (int i = 0; i < NR4; ++i) {
+                acc[hh][i][0] *= alpha; acc[hh][i][1] *= alpha; acc[hh][i][2] *= alpha; acc[hh][i][3] *= alpha;
+            }
+            m[hh] = m_new;
+        }
+        __syncwarp();
+        *reinterpret_cast<float4*>(pw + lane * AL_HW) = make_float4(p[0], p[1], p[2], p[3]);
+        __syncwarp();
+        for (int jj = 0; jj < n; ++jj) {
+            const float4 p4 = *reinterpret_cast<const float4*>(pw + jj * AL_HW);
+            const float pj[AL_HW] = {p4.x, p4.y, p4.z, p4.w};
+            const float* vr = k_s + jj * ld;
+#pragma unroll
+            for (int i = 0; i < NR4; ++i) {
+                const int d = 4 * (lane + 32 * i);
+                if (d < C) {
+                    const float4 v4 = *reinterpret_cast<const float4*>(vr + d);
+#pragma unroll
+                    for (int hh = 0; hh < AL_HW; ++hh) {
+                        acc[hh][i][0] = fmaf(pj[hh], v4.x, acc[hh][i][0]);
+                        acc[hh][i][1] = fmaf(pj[hh], v4.y, acc[hh][i][1]);
+                        acc[hh][i][2] = fmaf(pj[hh], v4.z, acc[hh][i][2]);
+                        acc[hh][i][3] = fmaf(pj[hh], v4.w, acc[hh][i][3]);
+                    }
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int hh = 0; hh < AL_HW; ++hh) {
+        const int h = hw0 + hh;
+        if (h >= H) continue;
+        if (runs == 1) {
+            const float inv = 1.f / l[hh];   // (a token always sees itself: l > 0)
+            T* dst = out + ((size_t)t * H + h) * C;
+#pragma unroll
+            for (int i = 0; i < NR4; ++i)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int d = 4 * (lane + 32 * i) + c;
+                    if (d < C) dst[d] = from_f32<T>(acc[hh][i][c] * inv);
+                }
+            continue;
+        }
+        float* dst = scratch + (((size_t)t * H + h) * runs + run) * (C + 2);
+        if (lane == 0) { dst[0] = m[hh]; dst[1] = l[hh]; }
+#pragma unroll
+        for (int i = 0; i < NR4; ++i)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const int d = 4 * (lane + 32 * i) + c;
+                if (d < C) dst[2 + d] = acc[hh][i][c];
+            }
     }
 }
 
-// One block per (token, head): the runs' parts added in run order.
+// One block per (token, head): the runs' parts added in run order.  Every run's weight exp(m_r - M) / L is formed once, in
+// shared memory (runs <= AL_MAX_RUNS); a channel's sum then has all its reads in flight together.
+#define AL_MAX_RUNS 1024
 template <typename T>
 __global__ void latent_attention_join_kernel(const float* __restrict__ scratch, T* __restrict__ out, int H, int C, int runs) {
+    __shared__ float w_s[AL_MAX_RUNS];
+    __shared__ float l_s[AL_MAX_RUNS];
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x, h = blockIdx.y;
     const float* src = scratch + ((size_t)t * H + h) * runs * (C + 2);
-    float M = -INFINITY;
-    for (int r = 0; r < runs; ++r) M = fmaxf(M, src[(size_t)r * (C + 2)]);
-    float L = 0.f;
-    for (int r = 0; r < runs; ++r) {
-        const float mr = src[(size_t)r * (C + 2)];
-        if (mr != -INFINITY) L += src[(size_t)r * (C + 2) + 1] * expf(mr - M);
+    for (int r = threadIdx.x; r < runs; r += blockDim.x) {
+        w_s[r] = src[(size_t)r * (C + 2)];
+        l_s[r] = src[(size_t)r * (C + 2) + 1];
     }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int r = 0; r < runs; ++r) M = fmaxf(M, w_s[r]);
+    float L = 0.f;
+    for (int r = 0; r < runs; ++r)
+        if (w_s[r] != -INFINITY) L += l_s[r] * expf(w_s[r] - M);
+    __syncthreads();
+    for (int r = threadIdx.x; r < runs; r += blockDim.x) w_s[r] = w_s[r] != -INFINITY ? expf(w_s[r] - M) / L : 0.f;
+    __syncthreads();
     for (int d = threadIdx.x; d < C; d += blockDim.x) {
         float o = 0.f;
-        for (int r = 0; r < runs; ++r) {
-            const float mr = src[(size_t)r * (C + 2)];
-            if (mr != -INFINITY) o += src[(size_t)r * (C + 2) + 2 + d] * expf(mr - M);
-        }
-        out[((size_t)t * H + h) * C + d] = from_f32<T>(o / L);
+#pragma unroll 8
+        for (int r = 0; r < runs; ++r) o = fmaf(w_s[r], src[(size_t)r * (C + 2) + 2 + d], o);
+        out[((size_t)t * H + h) * C + d] = from_f32<T>(o);
     }
 }
 
@@ -130,20 +216,21 @@ template <typename T>
 static int launch_latent_attention(const T* qa, const T* pool, const int* block_table, int max_blocks, const int* seq_of_token,
                                    const int* positions, T* out, float* scratch, float scale, int tokens, int H, int C, int R,
                                    int S, int runs, cudaStream_t stream) {
-    const int W = C + R;
-    const size_t smem = sizeof(float) * ((size_t)AL_TILE * (W | 1) + (size_t)AL_WARPS * W);
-    const size_t smem_max = sizeof(float) * ((size_t)AL_TILE * 1025 + (size_t)AL_WARPS * 1024);
-    dim3 grid(tokens, (H + AL_WARPS - 1) / AL_WARPS, runs);
-    static bool configured[3][VX_MAX_DEVICES];
-#define AL_GO(NR, SLOT)                                                                                               \
+    const int W = C + R, Wp = (W + 3) & ~3;
+    const size_t smem = sizeof(float) * ((size_t)AL_TILE * al_row_stride(W) + (size_t)AL_HEADS * Wp + AL_WARPS * AL_TILE * AL_HW);
+    const size_t smem_max = sizeof(float) * ((size_t)AL_TILE * al_row_stride(1024) + (size_t)AL_HEADS * 1024 + AL_WARPS * AL_TILE * AL_HW);
+    dim3 grid(tokens, (H + AL_HEADS - 1) / AL_HEADS, runs);
+    static bool configured[4][VX_MAX_DEVICES];
+#define AL_GO(NR4, SLOT)                                                                                              \
     do {                                                                                                              \
-        if (int rc = vx_configure_smem(latent_attention_kernel<T, NR>, smem_max, configured[SLOT])) return rc;         \
-        VX_LAUNCH_K(VX_K_ATTENTION, (latent_attention_kernel<T, NR>), grid, AL_WARPS * 32, smem, stream, qa, pool,     \
+        if (int rc = vx_configure_smem(latent_attention_kernel<T, NR4>, smem_max, configured[SLOT])) return rc;        \
+        VX_LAUNCH_K(VX_K_ATTENTION, (latent_attention_kernel<T, NR4>), grid, AL_WARPS * 32, smem, stream, qa, pool,    \
                     block_table, max_blocks, seq_of_token, positions, out, scratch, scale, H, C, R, S, runs);          \
     } while (0)
-    if (C <= 256) AL_GO(8, 0);
-    else if (C <= 512) AL_GO(16, 1);
-    else AL_GO(32, 2);
+    if (C <= 128) AL_GO(1, 0);
+    else if (C <= 256) AL_GO(2, 1);
+    else if (C <= 512) AL_GO(4, 2);
+    else AL_GO(8, 3);
 #undef AL_GO
     if (runs > 1)
         VX_LAUNCH_K(VX_K_JOIN, (latent_attention_join_kernel<T>), dim3(tokens, H), C >= 256 ? 128 : 64, 0, stream,
@@ -159,9 +246,9 @@ extern "C" int vx_latent_attention(const void* qa, const void* pool, const int* 
                                    const int* seq_of_token, const int* positions, void* out, float* scratch, float scale,
                                    int tokens, int H, int C, int R, int S, int runs, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
-    if (H <= 0 || C <= 0 || R < 0 || S <= 0 || max_blocks <= 0 || C + R > 1024 || runs < 1) return VX_ERR_SHAPE;
+    if (H <= 0 || C <= 0 || R < 0 || S <= 0 || max_blocks <= 0 || C + R > 1024 || runs < 1 || runs > AL_MAX_RUNS) return VX_ERR_SHAPE;
     if (runs > 1 && !scratch) return VX_ERR_SHAPE;
-    if ((H + AL_WARPS - 1) / AL_WARPS > 65535 || runs > 65535) return VX_ERR_LIMIT;
+    if ((H + AL_HEADS - 1) / AL_HEADS > 65535 || runs > 65535) return VX_ERR_LIMIT;
     if (dtype == VX_F32)
         return launch_latent_attention<float>((const float*)qa, (const float*)pool, block_table, max_blocks, seq_of_token,
                                               positions, (float*)out, scratch, scale, tokens, H, C, R, S, runs, stream);

@@ -1004,7 +1004,8 @@ def latent_prep(down: torch.Tensor, q: torch.Tensor, qa: Optional[torch.Tensor],
 
 
 LATENT_ATTENTION_MAX_ROW = 1024
-LATENT_ATTENTION_MAX_RUNS = 16
+LATENT_ATTENTION_MAX_RUNS = 32
+LATENT_ATTENTION_BLOCK_HEADS = 16   # query heads that share a staged tile of rows
 
 
 def latent_attention(qa: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, seq_of_token, positions, scale: float,
@@ -1022,10 +1023,10 @@ def latent_attention(qa: torch.Tensor, pool: torch.Tensor, block_table: torch.Te
     _need(0 < width <= LATENT_ATTENTION_MAX_ROW, "latent_attention: rows of up to %d elements" % LATENT_ATTENTION_MAX_ROW)
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
           "latent_attention: int32 block table [requests, blocks]")
-    blocks = tokens * (-(-heads // 8))
+    blocks = tokens * (-(-heads // LATENT_ATTENTION_BLOCK_HEADS))
     runs, scratch = 1, None
     if max_kv > 0 and blocks < 2 * _sm_count(qa.device):
-        runs = max(1, min(LATENT_ATTENTION_MAX_RUNS, 2 * _sm_count(qa.device) // blocks, -(-max_kv // 128)))
+        runs = max(1, min(LATENT_ATTENTION_MAX_RUNS, 2 * _sm_count(qa.device) // blocks, -(-max_kv // 64)))
         if runs > 1:
             scratch = workspace(qa.device, tokens * heads * runs * (rank + 2), which="latent_attention")
     out = torch.empty((tokens, heads, rank), dtype=qa.dtype, device=qa.device)
