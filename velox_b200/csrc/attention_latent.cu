@@ -44,6 +44,55 @@ __device__ __forceinline__ void al_stage_row<bf16>(float* dst, const bf16* src, 
     for (int d = lane; d < Wp; d += 32) dst[d] = d < W ? __bfloat162float(src[d]) : 0.f;
 }
 
+// ROWS rows (row i: `src[i]`, null: zeros) into shared memory rows `dst0 + i * dst_stride`.  bfloat16 rows of a multiple of 8
+// elements on 16-byte addresses: every load of the batch is issued before the first conversion, so the batch costs one
+// trip to memory.
+template <int ROWS>
+__device__ __forceinline__ void al_stage_rows(float* dst0, int dst_stride, const float* const (&src)[ROWS], int W, int Wp, int lane) {
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) {
+        float* dst = dst0 + i * dst_stride;
+        if (src[i]) al_stage_row<float>(dst, src[i], W, Wp, lane);
+        else for (int d = lane; d < Wp; d += 32) dst[d] = 0.f;
+    }
+}
+template <int ROWS>
+__device__ __forceinline__ void al_stage_rows(float* dst0, int dst_stride, const bf16* const (&src)[ROWS], int W, int Wp, int lane) {
+    bool fast = (W & 7) == 0;
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i) fast = fast && (((uintptr_t)src[i]) & 15) == 0;
+    if (!fast) {
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i) {
+            float* dst = dst0 + i * dst_stride;
+            if (src[i]) al_stage_row<bf16>(dst, src[i], W, Wp, lane);
+            else for (int d = lane; d < Wp; d += 32) dst[d] = 0.f;
+        }
+        return;
+    }
+    uint4 raw[ROWS][4];   // (rows of up to 1,024 elements: 4 pieces of 256)
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int d = lane * 8 + c * 256;
+            raw[i][c] = (src[i] && d < W) ? *reinterpret_cast<const uint4*>(src[i] + d) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+    for (int i = 0; i < ROWS; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const int d = lane * 8 + c * 256;
+            if (d >= W) continue;
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw[i][c]);
+            const float2 a = __bfloat1622float2(h2[0]), b = __bfloat1622float2(h2[1]);
+            const float2 e = __bfloat1622float2(h2[2]), f = __bfloat1622float2(h2[3]);
+            float* dst = dst0 + i * dst_stride + d;
+            *reinterpret_cast<float4*>(dst) = make_float4(a.x, a.y, b.x, b.y);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(e.x, e.y, f.x, f.y);
+        }
+}
+
 template <typename T, int NR4>
 __global__ void __launch_bounds__(AL_WARPS * 32)
 latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, const int* __restrict__ block_table,
@@ -65,13 +114,14 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
     const int per_run = (tiles + runs - 1) / runs;
     const int tile0 = run * per_run, tile1 = min(tiles, tile0 + per_run);
 
-    for (int hh = warp; hh < AL_HEADS; hh += AL_WARPS) {
-        float* dst = q_s + hh * Wp;
-        if (h0 + hh < H) {
-            al_stage_row<T>(dst, qa + ((size_t)t * H + h0 + hh) * W, W, Wp, lane);
-        } else {
-            for (int d = lane; d < Wp; d += 32) dst[d] = 0.f;
+    {
+        const T* src[AL_HEADS / AL_WARPS];
+#pragma unroll
+        for (int i = 0; i < AL_HEADS / AL_WARPS; ++i) {
+            const int hh = warp + i * AL_WARPS;
+            src[i] = h0 + hh < H ? qa + ((size_t)t * H + h0 + hh) * W : nullptr;
         }
+        al_stage_rows<AL_HEADS / AL_WARPS>(q_s + warp * Wp, AL_WARPS * Wp, src, W, Wp, lane);
     }
 
     float acc[AL_HW][NR4][4];
@@ -90,20 +140,21 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
         __syncthreads();   // the tile before this one has been used (and, the first time, the queries are written)
         const int my_page = lane < n ? bt[(j0 + lane) / S] : 0;   // (one trip to the table for the tile's 32 rows)
 #pragma unroll
-        for (int r8 = 0; r8 < AL_TILE / AL_WARPS; ++r8) {
-            const int r = warp + r8 * AL_WARPS;
-            const int page = __shfl_sync(0xffffffffu, my_page, r);
-            float* dst = k_s + r * ld;
-            if (r < n) {
-                al_stage_row<T>(dst, pool + ((size_t)page * S + ((j0 + r) % S)) * W, W, Wp, lane);
-            } else {
-                for (int d = lane; d < Wp; d += 32) dst[d] = 0.f;
+        for (int b = 0; b < AL_TILE / AL_WARPS; b += 4) {   // four rows of the warp's eight at a time
+            const T* src[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int r = warp + (b + i) * AL_WARPS;
+                const int page = __shfl_sync(0xffffffffu, my_page, r);
+                src[i] = r < n ? pool + ((size_t)page * S + ((j0 + r) % S)) * W : nullptr;
             }
+            al_stage_rows<4>(k_s + (warp + b * AL_WARPS) * ld, AL_WARPS * ld, src, W, Wp, lane);
         }
         __syncthreads();
         if (hw0 >= H) continue;
         float dot[AL_HW] = {0.f, 0.f, 0.f, 0.f};
         const float* kr = k_s + lane * ld;
+#pragma unroll 4
         for (int d = 0; d < Wp; d += 4) {
             const float4 k4 = *reinterpret_cast<const float4*>(kr + d);
 #pragma unroll
@@ -132,6 +183,7 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
         __syncwarp();
         *reinterpret_cast<float4*>(pw + lane * AL_HW) = make_float4(p[0], p[1], p[2], p[3]);
         __syncwarp();
+#pragma unroll 2
         for (int jj = 0; jj < n; ++jj) {
             const float4 p4 = *reinterpret_cast<const float4*>(pw + jj * AL_HW);
             const float pj[AL_HW] = {p4.x, p4.y, p4.z, p4.w};
@@ -206,7 +258,7 @@ __global__ void latent_attention_join_kernel(const float* __restrict__ scratch, 
     __syncthreads();
     for (int d = threadIdx.x; d < C; d += blockDim.x) {
         float o = 0.f;
-#pragma unroll 8
+#pragma unroll 16
         for (int r = 0; r < runs; ++r) o = fmaf(w_s[r], src[(size_t)r * (C + 2) + 2 + d], o);
         out[((size_t)t * H + h) * C + d] = from_f32<T>(o);
     }
@@ -233,8 +285,8 @@ static int launch_latent_attention(const T* qa, const T* pool, const int* block_
     else AL_GO(8, 3);
 #undef AL_GO
     if (runs > 1)
-        VX_LAUNCH_K(VX_K_JOIN, (latent_attention_join_kernel<T>), dim3(tokens, H), C >= 256 ? 128 : 64, 0, stream,
-                    (const float*)scratch, out, H, C, runs);
+        VX_LAUNCH_K(VX_K_JOIN, (latent_attention_join_kernel<T>), dim3(tokens, H), min(1024, (C + 31) / 32 * 32), 0, stream,
+                    (const float*)scratch, out, H, C, runs);   // (a thread per channel: its reads over the runs in flight together)
     VX_LAUNCH_CHECK();
     return VX_OK;
 }

@@ -68,22 +68,33 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
     for (int tb = t0; tb < t1; tb += LW_CHUNK) {
         const int n = min(LW_CHUNK, t1 - tb);
         __syncthreads();
-        for (int i = threadIdx.x; i < n * DP; i += LW_THREADS) {
+        // q and k of channels that are not turned take their multipliers here, the turned ones after the turn
+        auto stage = [&](int i) {
             const int tt = i / DP, d = i - tt * DP;
             float qv = 0.f, kv = 0.f, av = 1.f;
             if (d < D) {
                 const T* row = x + (size_t)(tb + tt) * ldx + (size_t)h * D + d;
-                qv = to_f32(row[q_col]);
-                kv = to_f32(row[k_col]);
+                const bool turned = inv_freq && d < rot_dim;
+                qv = to_f32(row[q_col]) * (turned ? 1.f : q_mul);
+                kv = to_f32(row[k_col]) * (turned ? 1.f : k_mul);
                 if (GATED) av = expf(gate_mul * log_sigmoid(gate[(size_t)(tb + tt) * ldg + (size_t)h * D + d]));
             }
             q_s[i] = qv;
             k_s[i] = kv;
             if (GATED) a_s[i] = av;
-        }
-        for (int i = threadIdx.x; i < n * LW_COLS; i += LW_THREADS) {
+        };
+        auto stage_v = [&](int i) {
             const int tt = i / LW_COLS, cc = i - tt * LW_COLS;
             v_s[i] = (col0 + cc < Dv) ? to_f32(x[(size_t)(tb + tt) * ldx + v_col + (size_t)h * Dv + col0 + cc]) : 0.f;
+        };
+        if (n == LW_CHUNK) {   // a whole chunk: a fixed number of rounds, so that a thread's loads are all in flight together
+#pragma unroll
+            for (int it = 0; it < LW_CHUNK * DP / LW_THREADS; ++it) stage(threadIdx.x + it * LW_THREADS);
+#pragma unroll
+            for (int it = 0; it < LW_CHUNK * LW_COLS / LW_THREADS; ++it) stage_v(threadIdx.x + it * LW_THREADS);
+        } else {
+            for (int i = threadIdx.x; i < n * DP; i += LW_THREADS) stage(i);
+            for (int i = threadIdx.x; i < n * LW_COLS; i += LW_THREADS) stage_v(i);
         }
         __syncthreads();
         if (inv_freq && half > 0) {
@@ -93,15 +104,11 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
                 sincosf((float)positions[tb + tt] * inv_freq[p], &sn, &cs);
                 const int ia = tt * DP + (interleaved ? 2 * p : p), ib = tt * DP + (interleaved ? 2 * p + 1 : p + half);
                 const float qa = q_s[ia], qb = q_s[ib], ka = k_s[ia], kb = k_s[ib];
-                q_s[ia] = qa * cs - qb * sn;
-                q_s[ib] = qb * cs + qa * sn;
-                k_s[ia] = ka * cs - kb * sn;
-                k_s[ib] = kb * cs + ka * sn;
+                q_s[ia] = (qa * cs - qb * sn) * q_mul;
+                q_s[ib] = (qb * cs + qa * sn) * q_mul;
+                k_s[ia] = (ka * cs - kb * sn) * k_mul;
+                k_s[ib] = (kb * cs + ka * sn) * k_mul;
             }
-            __syncthreads();
-        }
-        if (q_mul != 1.f || k_mul != 1.f) {
-            for (int i = threadIdx.x; i < n * DP; i += LW_THREADS) { q_s[i] *= q_mul; k_s[i] *= k_mul; }
             __syncthreads();
         }
         for (int tt = 0; tt < n; ++tt) {
