@@ -95,7 +95,19 @@ PLAIN = config(90, 64, [
                  mlp=dense(32, 1.5)),
 ])
 
-CONFIGS = {"odd": ODD, "even": EVEN, "plain": PLAIN}
+# sizes at the borders of the fast paths: a latent layer whose keys and values the tensor-core kernel takes but whose fused
+# projection has rows of 180 elements (no multiple of 8: it goes the folded way), one that goes the raised way with values of
+# another size than the first, linear attentions with heads of 72 and 136 channels (rows padded in shared memory), the whole
+# model gone through twice
+BORDERS = config(120, 96, [
+    latent(2, 32, 32, 32, 20, 0.2, 3000.0, dense(40, 1.0)),
+    gated(2, 72, 40, 9.0, 6, None),
+    latent(3, 32, 32, 64, 40, 0.15, 700.0, dense(56, 2.5)),
+    side_by_side(softmax_member(3, 1, 32, 32, 0.2, softcap=10.0, rot=(900.0, 16)),
+                 retention_member(1, 136, 24, [0.97], rot=(200.0, 40)), 1.1, 0.4, dense(32, 1.0)),
+], embedding_scale=0.75, logit_softcap=20.0, loop=(0, 4, 2))
+
+CONFIGS = {"odd": ODD, "even": EVEN, "plain": PLAIN, "borders": BORDERS}
 
 
 def tensor_shapes(cfg):

@@ -87,7 +87,8 @@ def test_the_stream_after_every_layer_run(models, name):
 
 
 @pytest.mark.parametrize("name,dtype,length", [("odd", "float32", 150), ("even", "float32", 150), ("plain", "float32", 100),
-                                               ("odd", "bfloat16", 150), ("even", "bfloat16", 150), ("plain", "bfloat16", 100)])
+                                               ("odd", "bfloat16", 150), ("even", "bfloat16", 150), ("plain", "bfloat16", 100),
+                                               ("borders", "float32", 150), ("borders", "bfloat16", 150)])
 def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation(models, name, dtype, length):
     cfg, w, folder = models[name]
     toks = tokens_of(cfg, length, 1)

@@ -62,6 +62,8 @@ class StepContext:
     # the step's rows cut into stretches for recurrences that walk a long portion's stretches side by side; made by the
     # first mixer that wants it
     walk_stretches: Optional[object] = None
+    # where the keys and values that a latent attention raises for this step's requests lie (`ops.RaisedPlan`), likewise
+    raised_rows: Optional[object] = None
 
     @property
     def decode_only(self) -> bool:

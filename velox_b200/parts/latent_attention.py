@@ -103,8 +103,10 @@ class LatentAttention(Mixer):
         q, down = x[:, :H * (D + R)], x[:, H * (D + R):]
         interleaved = bool(getattr(self.position, "interleaved", False))
         if (self.raise_w is not None and ctx.max_new >= RAISE_MIN_TOKENS and len(ctx.new_lens) == ctx.n_seqs
-                and len(ctx.offsets) == ctx.n_seqs):
-            plan = ops.RaisedPlan([a + b for a, b in zip(ctx.offsets, ctx.new_lens)], x.device)
+                and len(ctx.offsets) == ctx.n_seqs and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+            plan = getattr(ctx, "raised_rows", None)   # (made by the step's first latent layer, kept on its context)
+            if plan is None:
+                plan = ctx.raised_rows = ops.RaisedPlan([a + b for a, b in zip(ctx.offsets, ctx.new_lens)], x.device)
             if plan.rows * H * (D + R + Dv) * 2 <= RAISE_MAX_BYTES:
                 ops.latent_prep(down, q, None, self.norm_weight, self.eps, self.rotary[0], interleaved, ctx.positions,
                                 group.slot_mapping if cache.writes else None, cache.pages, H, D, R, C)
