@@ -110,6 +110,44 @@ BORDERS = config(120, 96, [
 CONFIGS = {"odd": ODD, "even": EVEN, "plain": PLAIN, "borders": BORDERS}
 
 
+def drawn_config(seed):
+    """A configuration drawn from `seed`: two to five layers of any kind in any order, sizes from lists that hold what every
+    kernel takes and what none does (latent rows of 32 to 584 elements, 1 to 17 heads, keys of 16 to 200 channels, values of
+    16 to 128), feed-forwards present or not, a loop over any run of layers one to three times, or none."""
+    rng = np.random.default_rng(1000 + seed)
+    pick = lambda xs: xs[int(rng.integers(0, len(xs)))]
+    width = pick([64, 96, 136, 200, 256])
+
+    def ff():
+        return None if rng.random() < 0.15 else dense(pick([32, 72, 128]), pick([0.75, 1.5, 4.0]))
+
+    def lat():
+        D, R = pick([(32, 32), (64, 64), (128, 64), (16, 16), (24, 8), (96, 32), (32, 64), (192, 64)])
+        Dv = pick([32, 64, 128, 20, D])
+        return latent(pick([1, 2, 5, 8, 17]), D, R, Dv, pick([24, 40, 96, 136, 264, 520]), pick([0.1, 0.2]), pick([100.0, 1e4, 5e5]), ff())
+
+    def gl():
+        return gated(pick([1, 2, 6]), pick([16, 48, 64, 100, 144, 200]), pick([16, 32, 40, 64, 72]), pick([1.0, 4.0, 16.0]), pick([2, 8]), ff())
+
+    def par():
+        D, G = pick([16, 32, 64, 128, 40]), pick([1, 2])
+        H = G * pick([1, 2, 3, 4])
+        Dv = pick([D, 32, 64]) if D in (64, 128) else D
+        left = softmax_member(H, G, D, Dv, pick([0.1, 0.2]), softcap=pick([None, 5.0, 30.0]), rot=(pick([1e4, 2e4]), pick([D, D // 2])))
+        Dr, Hr = pick([16, 32, 64, 136]), pick([1, 3, 6])
+        right = retention_member(Hr, Dr, pick([16, 32, 24]), [1.0 - 2.0 ** -float(rng.integers(3, 10)) for _ in range(Hr)],
+                                 rot=None if rng.random() < 0.2 else (pick([1e4, 1e6]), pick([Dr, Dr // 2]) // 2 * 2))
+        return side_by_side(left, right, pick([None, 0.8]), pick([None, 0.9]), ff())
+
+    n = int(rng.integers(2, 6))
+    layers = [pick([lat, gl, par])() for _ in range(n)]
+    loop = None
+    if rng.random() < 0.6:
+        a = int(rng.integers(0, n))
+        loop = (a, int(rng.integers(a + 1, n + 1)), int(rng.integers(1, 4)))
+    return config(pick([64, 300]), width, layers, embedding_scale=pick([None, 0.5]), logit_softcap=pick([None, 15.0]), loop=loop)
+
+
 def tensor_shapes(cfg):
     E, out = cfg["width"], {}
     out["embed"] = (cfg["vocab"], E)

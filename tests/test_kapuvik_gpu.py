@@ -7,7 +7,7 @@ import numpy as np
 import pytest
 
 import plain_kapuvik as K
-from kapuvik_helpers import CONFIGS, Oracle, compare, lively_weights, write_model
+from kapuvik_helpers import CONFIGS, Oracle, compare, drawn_config, lively_weights, write_model
 from helpers import RoundingJudge, assert_close
 
 pytestmark = pytest.mark.gpu
@@ -107,6 +107,37 @@ def test_whole_prompts_portions_and_decoding_agree_with_the_plain_implementation
     for what, steps in ways.items():
         got = np.concatenate([g for g in run(engine, steps + [[("end", "a")]]) if g is not None])
         compare(got, [(oracle, 0, len(got))], dtype, "%s, %s" % (name, what), judge)
+    if dtype != "float32":
+        judge.finish()
+
+
+@pytest.mark.parametrize("seed", range(8))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_configurations_drawn_at_random(tmp_path, seed, dtype):
+    """Other sizes, layer orders and loops than the fixed configurations have: a request of 200 tokens whole, in portions of
+    2 to 130 tokens, as a prompt followed by single tokens, and three unequal requests that join and leave a batch."""
+    cfg = drawn_config(seed)
+    w = lively_weights(cfg, seed=seed)
+    folder = write_model(str(tmp_path / "drawn"), cfg, w)
+    a, b, c = [tokens_of(cfg, n, seed * 7 + i) for i, n in enumerate((200, 90, 33))]
+    oa, ob, oc = Oracle(cfg, w, a), Oracle(cfg, w, b), Oracle(cfg, w, c)
+    judge = RoundingJudge.of([oa, ob, oc], "kapuvik drawn %d %s" % (seed, dtype))
+    engine = engine_for(folder, dtype, 384)
+    ways = {"whole": [[("a", a, list(range(len(a))))]],
+            "portions": portions(a, [2, 64, 5, 1, 16, 130], "a"),
+            "prompt then single tokens": [[("a", a[:150], list(range(150)))]] + [[("a", [t], [0])] for t in a[150:]]}
+    for what, steps in ways.items():
+        got = np.concatenate([g for g in run(engine, steps + [[("end", "a")]]) if g is not None])
+        compare(got, [(oa, 0, len(got))], dtype, "drawn %d, %s" % (seed, what), judge)
+    steps = [[("a", a[:40], list(range(40))), ("b", b[:60], list(range(60)))],
+             [("a", a[40:41], [0]), ("b", b[60:90], list(range(30))), ("c", c[:20], list(range(20)))],
+             [("a", a[41:100], list(range(59))), ("c", c[20:21], [0])],
+             [("end", "b"), ("c", c[21:33], list(range(12))), ("a", a[100:101], [0])]]
+    rows = [[(oa, 0, 40), (ob, 0, 60)], [(oa, 40, 41), (ob, 60, 90), (oc, 0, 20)], [(oa, 41, 100), (oc, 20, 21)],
+            [(oc, 21, 33), (oa, 100, 101)]]
+    got = [g for g in run(engine, steps + [[("end", "a"), ("end", "c")]]) if g is not None]
+    for g, r in zip(got, rows):
+        compare(g, r, dtype, "drawn %d, a batch that requests join and leave" % seed, judge)
     if dtype != "float32":
         judge.finish()
 
