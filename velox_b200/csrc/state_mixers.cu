@@ -35,6 +35,21 @@ __device__ __forceinline__ float log_sigmoid(float z) { return fminf(z, 0.f) - l
 // exp(gate_mul * log_sigmoid(gate[t, h D + d])): sigmoid(z)^(gate_mul), formed through the logarithm.  A token's output
 // column is summed over a thread's rows in order, then over the 4 row groups of a warp by two exchanges, then over the warps
 // in warp order (through shared memory, once a chunk): an order fixed by D alone.
+__device__ __forceinline__ void lw_load8(const float* p, float (&v)[8]) {
+    const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+__device__ __forceinline__ void lw_load8(const bf16* p, float (&v)[8]) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(h2[e]);
+        v[2 * e] = f.x;
+        v[2 * e + 1] = f.y;
+    }
+}
+
 template <typename T, int R, bool GATED>
 __global__ void __launch_bounds__(LW_THREADS, 4)
 linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_col, int v_col,
@@ -55,6 +70,8 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
     const int cg = lane & 7, row0 = (warp * 4 + (lane >> 3)) * R, c0 = col0 + cg * LW_CC;
     const float dec = GATED ? 1.f : decay[h];
     const int half = rot_dim >> 1;
+    const bool by_eights = (D & 7) == 0 && ((size_t)ldx * sizeof(T) & 15) == 0 && (((uintptr_t)(x + q_col)) & 15) == 0 &&
+                           (((uintptr_t)(x + k_col)) & 15) == 0 && (!GATED || ((ldg & 3) == 0 && (((uintptr_t)gate) & 15) == 0));
     pdl_wait();
     pdl_trigger();
     const int t0 = cu_seqlens[seq], t1 = cu_seqlens[seq + 1];
@@ -87,7 +104,44 @@ linear_attention_walk_kernel(const T* __restrict__ x, int ldx, int q_col, int k_
             const int tt = i / LW_COLS, cc = i - tt * LW_COLS;
             v_s[i] = (col0 + cc < Dv) ? to_f32(x[(size_t)(tb + tt) * ldx + v_col + (size_t)h * Dv + col0 + cc]) : 0.f;
         };
-        if (n == LW_CHUNK) {   // a whole chunk: a fixed number of rounds, so that a thread's loads are all in flight together
+        // eight channels at a time where rows, columns and sizes lie on 16-byte borders
+        auto stage8 = [&](int g) {
+            const int tt = g / (DP / 8), d = (g - tt * (DP / 8)) * 8;
+            float qv[8], kv[8], av[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { qv[e] = 0.f; kv[e] = 0.f; av[e] = 1.f; }
+            if (d < D) {
+                const T* row = x + (size_t)(tb + tt) * ldx + (size_t)h * D + d;
+                lw_load8(row + q_col, qv);
+                lw_load8(row + k_col, kv);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    const bool turned = inv_freq && d + e < rot_dim;
+                    qv[e] *= turned ? 1.f : q_mul;
+                    kv[e] *= turned ? 1.f : k_mul;
+                }
+                if (GATED) {
+                    lw_load8(gate + (size_t)(tb + tt) * ldg + (size_t)h * D + d, av);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) av[e] = expf(gate_mul * log_sigmoid(av[e]));
+                }
+            }
+            const int i = tt * DP + d;
+            *reinterpret_cast<float4*>(q_s + i) = make_float4(qv[0], qv[1], qv[2], qv[3]);
+            *reinterpret_cast<float4*>(q_s + i + 4) = make_float4(qv[4], qv[5], qv[6], qv[7]);
+            *reinterpret_cast<float4*>(k_s + i) = make_float4(kv[0], kv[1], kv[2], kv[3]);
+            *reinterpret_cast<float4*>(k_s + i + 4) = make_float4(kv[4], kv[5], kv[6], kv[7]);
+            if (GATED) {
+                *reinterpret_cast<float4*>(a_s + i) = make_float4(av[0], av[1], av[2], av[3]);
+                *reinterpret_cast<float4*>(a_s + i + 4) = make_float4(av[4], av[5], av[6], av[7]);
+            }
+        };
+        if (n == LW_CHUNK && by_eights) {
+#pragma unroll
+            for (int it = 0; it < LW_CHUNK * DP / 8 / LW_THREADS; ++it) stage8(threadIdx.x + it * LW_THREADS);
+#pragma unroll
+            for (int it = 0; it < LW_CHUNK * LW_COLS / LW_THREADS; ++it) stage_v(threadIdx.x + it * LW_THREADS);
+        } else if (n == LW_CHUNK) {   // a whole chunk: a fixed number of rounds, so that a thread's loads are all in flight together
 #pragma unroll
             for (int it = 0; it < LW_CHUNK * DP / LW_THREADS; ++it) stage(threadIdx.x + it * LW_THREADS);
 #pragma unroll
