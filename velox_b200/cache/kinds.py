@@ -90,13 +90,14 @@ class PagedKVKind(CacheKind):
         return spec.keep_first if spec.window > 0 else 0
 
     def page_bytes(self, spec: PagedKV, page_size, element_bytes):
-        return spec.num_kv_heads * (spec.head_dim + spec.value_dim) * page_size * element_bytes
+        return (spec.num_kv_heads * spec.head_dim + spec.value_heads * spec.value_dim) * page_size * element_bytes
 
     def allocate(self, spec: PagedKV, layers, num_pages, page_size, dtype, device):
-        if spec.value_dim == spec.head_dim:
+        if spec.value_dim == spec.head_dim and spec.value_heads == spec.num_kv_heads:
             return torch.empty((layers, 2, num_pages, spec.num_kv_heads, page_size, spec.head_dim), dtype=dtype, device=device)
-        cells = num_pages * spec.num_kv_heads * page_size
-        return torch.empty((layers, cells * (spec.head_dim + spec.value_dim)), dtype=dtype, device=device)
+        cells = num_pages * page_size
+        return torch.empty((layers, cells * (spec.num_kv_heads * spec.head_dim + spec.value_heads * spec.value_dim)),
+                           dtype=dtype, device=device)
 
     def layer_cache(self, storage, index, group):
         if storage is None:
@@ -106,10 +107,11 @@ class PagedKVKind(CacheKind):
     def layer_cache_of(self, spec: PagedKV, storage, index, group, page_size):
         if storage is None or storage.dim() != 2:
             return self.layer_cache(storage, index, group)
-        cells = storage.shape[1] // (spec.head_dim + spec.value_dim)   # pages * kv heads * page size
+        k_row, v_row = spec.num_kv_heads * spec.head_dim, spec.value_heads * spec.value_dim
+        cells = storage.shape[1] // (k_row + v_row)   # pages * page size
         flat = storage[index]
-        k = flat[:cells * spec.head_dim].view(-1, spec.num_kv_heads, page_size, spec.head_dim)
-        v = flat[cells * spec.head_dim:].view(-1, spec.num_kv_heads, page_size, spec.value_dim)
+        k = flat[:cells * k_row].view(-1, spec.num_kv_heads, page_size, spec.head_dim)
+        v = flat[cells * k_row:].view(-1, spec.value_heads, page_size, spec.value_dim)
         return LayerCache(group, True, k, v, None, flat)
 
 
@@ -117,6 +119,9 @@ class PagedLatentKind(CacheKind):
     """One row per position: [layer, page, 1, offset in page, width].  The mixer is handed the same tensor as
     `k_pool` and `v_pool` (and `pages`): an attention kernel reads it as one key/value head whose value is
     the first part of the key's row."""
+
+    def window(self, spec: PagedLatent) -> int:
+        return spec.window
 
     def page_bytes(self, spec: PagedLatent, page_size, element_bytes):
         return spec.width * page_size * element_bytes

@@ -1,11 +1,11 @@
 from .engine_config import EngineConfig
-from .model_config import (BuvuzenConfig, ConfigError, DobepelConfig, KapuvikConfig, ModelConfig, Qwen3Config,
+from .model_config import (BuvuzenConfig, ConfigError, DobepelConfig, FovenexConfig, KapuvikConfig, ModelConfig, Qwen3Config,
                            read_config_json)
 from .registry import (Architecture, load_config, register_architecture, registered_architectures,
                        resolve_architecture, unregister_architecture)
 
 __all__ = [
-    "EngineConfig", "BuvuzenConfig", "ConfigError", "DobepelConfig", "KapuvikConfig", "ModelConfig", "Qwen3Config", "read_config_json", "Architecture",
+    "EngineConfig", "BuvuzenConfig", "ConfigError", "DobepelConfig", "FovenexConfig", "KapuvikConfig", "ModelConfig", "Qwen3Config", "read_config_json", "Architecture",
     "load_config", "register_architecture", "registered_architectures", "resolve_architecture",
     "unregister_architecture",
 ]

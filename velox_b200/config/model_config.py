@@ -594,3 +594,165 @@ class KapuvikConfig(ModelConfig):
                 number(at + ".mlp", mlp, "limit", 0)
         if faults:
             raise ConfigError("Kapuvik configuration: " + "; ".join(faults))
+
+
+@dataclass(frozen=True)
+class FovenexConfig(ModelConfig):
+    """Fovenex: a decoder whose config.json is nested and lists its layers one by one.
+
+        architecture   "Fovenex"
+        vocab, width, norm.eps
+        residual_mult  multiplier of every sublayer's output on its way into the stream (absent: 1)
+        streams        copies of the stream with learned mixing (absent or 0: one stream, no mixing tensors)
+        layers[i]      type "attention":         mixer (heads, kv_heads, dim, vdim, scale, diff, rot.base, rot.dims,
+                                                 rot.scaling.{factor, original, fast, slow} (optional), mask.size (optional))
+                       type "latent_attention":  mixer (heads, dim, rot_dim, vdim, kv_rank, scale, rot.base,
+                                                 q_rank (optional: queries through a latent of their own),
+                                                 mask.size (optional window), kv_from (optional: the layer whose cached
+                                                 rows it reads instead of making its own))
+                       mlp: null | kind "dense" (ff)
+
+    Every size and constant is read from there; the layers may differ from one another."""
+
+    architecture: ClassVar[str] = "Fovenex"
+    model_type: ClassVar[str] = "fovenex"
+    LAYER_TYPES: ClassVar[Tuple[str, ...]] = ("attention", "latent_attention")
+
+    vocab: int = _field(int)
+    width: int = _field(int)
+    norm_eps: float = _field(float)
+    residual_mult: float = _field(float, default=1.0)
+    streams: int = _field(int, default=0)
+    layers: Tuple[Dict[str, Any], ...] = _field(tuple, default=())
+
+    @classmethod
+    def from_dict(cls, raw: Dict[str, Any]) -> "FovenexConfig":
+        faults: list = []
+
+        def get(d, path, kind, default=dataclasses.MISSING):
+            cur = d
+            for key in path.split("."):
+                if not isinstance(cur, dict) or cur.get(key) is None:
+                    if default is dataclasses.MISSING:
+                        faults.append("missing key %r" % path)
+                    return None if default is dataclasses.MISSING else default
+                cur = cur[key]
+            return _typed(path, cur, kind, faults)
+
+        values = dict(vocab=get(raw, "vocab", int), width=get(raw, "width", int), norm_eps=get(raw, "norm.eps", float),
+                      residual_mult=get(raw, "residual_mult", float, 1.0), streams=get(raw, "streams", int, 0))
+        layers = raw.get("layers")
+        if not isinstance(layers, list) or not layers:
+            faults.append("key 'layers': expected a list of layers")
+            layers = []
+        if faults:
+            raise ConfigError("config.json for %s: %s" % (cls.__name__, "; ".join(faults)))
+        cfg = cls(layers=tuple(json.loads(json.dumps(layer)) for layer in layers), **values)
+        cfg.validate()
+        return cfg
+
+    def to_dict(self) -> Dict[str, Any]:
+        out = {"architecture": self.architecture, "layers": json.loads(json.dumps(list(self.layers))),
+               "norm": {"eps": self.norm_eps}, "residual_mult": self.residual_mult, "vocab": self.vocab, "width": self.width}
+        if self.streams:
+            out["streams"] = self.streams
+        return out
+
+    @staticmethod
+    def window_of(mixer: Dict[str, Any]) -> int:
+        mask = mixer.get("mask")
+        return int(mask.get("size") or 0) if isinstance(mask, dict) else 0
+
+    def rows_source(self, i: int) -> Optional[int]:
+        """The layer whose cached latent rows layer i reads, or None if it keeps its own (or is no latent layer)."""
+        m = self.layers[i].get("mixer") or {}
+        return m.get("kv_from") if self.layers[i].get("type") == "latent_attention" else None
+
+    def validate(self) -> None:
+        faults = []
+
+        def positive(where, d, *keys):
+            ok = True
+            for k in keys:
+                v = d.get(k) if isinstance(d, dict) else None
+                if not isinstance(v, int) or isinstance(v, bool) or v <= 0:
+                    faults.append("%s.%s must be a positive integer, got %r" % (where, k, v))
+                    ok = False
+            return ok
+
+        def number(where, d, key, least=None):
+            v = d.get(key) if isinstance(d, dict) else None
+            if not isinstance(v, (int, float)) or isinstance(v, bool) or (least is not None and not v > least):
+                faults.append("%s.%s must be a number%s, got %r" % (where, key, "" if least is None else " above %g" % least, v))
+                return False
+            return True
+
+        def window(where, m):
+            mask = m.get("mask")
+            if mask is not None and (not isinstance(mask, dict) or not positive(where + ".mask", mask, "size")):
+                if not isinstance(mask, dict):
+                    faults.append("%s.mask must hold a size, got %r" % (where, mask))
+
+        for name in ("vocab", "width"):
+            if getattr(self, name) <= 0:
+                faults.append("%s must be positive, got %d" % (name, getattr(self, name)))
+        if not self.norm_eps > 0:
+            faults.append("norm.eps must be positive, got %r" % self.norm_eps)
+        if not 0 <= self.streams <= 16:
+            faults.append("streams must lie in 0 .. 16, got %r" % self.streams)
+        for i, layer in enumerate(self.layers):
+            at = "layers[%d]" % i
+            if not isinstance(layer, dict) or layer.get("type") not in self.LAYER_TYPES:
+                faults.append("%s.type %r is not one of %s" % (at, layer.get("type") if isinstance(layer, dict) else layer,
+                                                               list(self.LAYER_TYPES)))
+                continue
+            m, kind = layer.get("mixer"), layer["type"]
+            where = at + ".mixer"
+            if kind == "attention":
+                if positive(where, m, "heads", "kv_heads", "dim", "vdim"):
+                    if m["heads"] % m["kv_heads"]:
+                        faults.append("%s: heads (%d) is not a multiple of kv_heads (%d)" % (where, m["heads"], m["kv_heads"]))
+                    number(where, m, "scale")
+                    if number(where, m, "diff") and not 0 <= m["diff"] < 1:
+                        faults.append("%s.diff must lie in [0, 1), got %r" % (where, m["diff"]))
+                    rot = m.get("rot")
+                    if rot is not None:
+                        if not isinstance(rot, dict) or not positive(where + ".rot", rot, "dims") or not number(where + ".rot", rot, "base", 1):
+                            pass
+                        elif rot["dims"] % 2 or rot["dims"] > m["dim"]:
+                            faults.append("%s.rot.dims (%d) must be even and within the head's %d channels" % (where, rot["dims"], m["dim"]))
+                        sc = rot.get("scaling") if isinstance(rot, dict) else None
+                        if sc is not None:
+                            for key in ("factor", "original", "fast", "slow"):
+                                number(where + ".rot.scaling", sc, key, 0)
+                    window(where, m)
+            else:
+                if positive(where, m, "heads", "dim", "rot_dim", "vdim", "kv_rank"):
+                    number(where, m, "scale")
+                    if m["rot_dim"] % 2:
+                        faults.append("%s.rot_dim (%d) must be even" % (where, m["rot_dim"]))
+                    if not isinstance(m.get("rot"), dict) or not number(where + ".rot", m.get("rot"), "base", 1):
+                        pass
+                    elif m["rot"].get("dims", m["rot_dim"]) != m["rot_dim"]:
+                        faults.append("%s.rot.dims must equal rot_dim" % where)
+                    if m.get("q_rank") is not None:
+                        positive(where, m, "q_rank")
+                    window(where, m)
+                    j = m.get("kv_from")
+                    if j is not None:
+                        src = self.layers[j] if isinstance(j, int) and not isinstance(j, bool) and 0 <= j < i else None
+                        sm = src.get("mixer") if isinstance(src, dict) and src.get("type") == "latent_attention" else None
+                        if not isinstance(sm, dict) or sm.get("kv_from") is not None:
+                            faults.append("%s.kv_from %r must name an earlier latent layer that keeps rows of its own" % (where, j))
+                        elif (sm.get("kv_rank"), sm.get("rot_dim"), (sm.get("rot") or {}).get("base")) != \
+                                (m["kv_rank"], m["rot_dim"], (m.get("rot") or {}).get("base")):
+                            faults.append("%s.kv_from %d: kv_rank, rot_dim and rotation must equal that layer's" % (where, j))
+            mlp = layer.get("mlp")
+            if mlp is None:
+                continue
+            if not isinstance(mlp, dict) or mlp.get("kind") != "dense":
+                faults.append("%s.mlp.kind %r is not 'dense'" % (at, mlp.get("kind") if isinstance(mlp, dict) else mlp))
+            else:
+                positive(at + ".mlp", mlp, "ff")
+        if faults:
+            raise ConfigError("Fovenex configuration: " + "; ".join(faults))

@@ -44,10 +44,13 @@ __host__ __device__ constexpr int ab_chunks(int n) { return n % 8 == 0 ? n : ab_
 //   k + page * k_page + hk * k_head + (j % S) * k_row,   page = table[j / S]
 // (a page pool [pages, kv heads, S, size] has k_page = Hk S size, k_head = S size, k_row = size; rows [n, heads, sizes]
 // that a matrix product left have k_row = the row's length and k_head = one head's share of it).  With `table_by_segment`
-// the block table's row is the segment's number, not the request's.
+// the block table's row is the segment's number, not the request's.  With `v_share` > 1 that many consecutive key heads
+// read one value head (v_page and v_head then count value heads); with `out_f32` the output is written as float32.
 struct AbLayout {
     long long k_page, k_head, k_row, v_page, v_head, v_row;
     int table_by_segment;
+    int v_share;
+    int out_f32;
 };
 
 template <int CH> __device__ __forceinline__ int ab_swz(int r, int cc) {
@@ -122,6 +125,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
     const int hk = share > 1 ? blockIdx.y : blockIdx.y / (H / Hk);
     const int head0 = share > 1 ? hk * share : blockIdx.y;
     const int* bt = block_table + (size_t)(lay.table_by_segment ? s : seq) * max_blocks;
+    const int hv = lay.v_share > 1 ? hk / lay.v_share : hk;
     const int toks_live = min(toks_per_tile, n_new - t0);
     const int kv_hi = off + t0 + toks_live;                              // one past the tile's last visible key
     const int kv_lo = window > 0 ? max(0, off + t0 + 1 - window) : 0;    // first key of the first row's window
@@ -165,7 +169,7 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
             key = min(key, kv_hi - 1);
             const int page = bt[key / S];
             cp_async16(vs + r * VROW + (ab_swz<VCHP>(r, cc) << 4),
-                       v_pool + (size_t)page * lay.v_page + (size_t)hk * lay.v_head + (size_t)(key % S) * lay.v_row + cc * 8);
+                       v_pool + (size_t)page * lay.v_page + (size_t)hv * lay.v_head + (size_t)(key % S) * lay.v_row + cc * 8);
         }
     };
     issue(0, 0);
@@ -338,7 +342,15 @@ biased_attention_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16
         if (sinks) ab_add_sink(sinks[hd] * AB_LOG2E, m[hrow], l[hrow], f);
         if (gate_col >= 0) f *= ab_gate(q, q_row_stride, row_base + t0 + tok, gate_col, hd);
         const float inv = f / l[hrow];
-        bf16* dst = out + (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)hd * DV + ((lane & 3) << 1);
+        const size_t at = (size_t)(row_base + t0 + tok) * out_row_stride + (size_t)hd * DV + ((lane & 3) << 1);
+        if (lay.out_f32) {
+            float* dst = reinterpret_cast<float*>(out) + at;
+#pragma unroll
+            for (int nt = 0; nt < DV / 8; ++nt)
+                *reinterpret_cast<float2*>(dst + nt * 8) = make_float2(o[nt][2 * hrow] * inv, o[nt][2 * hrow + 1] * inv);
+            continue;
+        }
+        bf16* dst = out + at;
 #pragma unroll
         for (int nt = 0; nt < DV / 8; ++nt)
             *reinterpret_cast<__nv_bfloat162*>(dst + nt * 8) =
@@ -361,7 +373,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
                      const int* __restrict__ seq_of_token, const int* __restrict__ positions, bf16* __restrict__ out,
                      int out_row_stride, float scale_log2, float bias_exp, int window, int keep_first, int H, int Hk,
                      int S, int share_log2, float* __restrict__ scratch, const float* __restrict__ sinks, int gate_col,
-                     float cap_log2, float cap_arg) {
+                     float cap_log2, float cap_arg, int v_share, int out_f32) {
     extern __shared__ __align__(128) unsigned char ad_smem[];
     constexpr int KCH = DK / 8, VCH = DV / 8;
     constexpr int KCHP = ab_pow2(KCH), VCHP = ab_pow2(VCH);
@@ -414,7 +426,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
             const int key = n < nkept ? n : start + n - nkept;
             const int page = bt[key / S];
             cp_async16(vs + r * VROW + (ab_swz<VCHP>(r, cc) << 4),
-                       v_pool + (((size_t)page * Hk + hk) * S + (key % S)) * DV + cc * 8);
+                       v_pool + (((size_t)page * (Hk / v_share) + hk / v_share) * S + (key % S)) * DV + cc * 8);
         }
     };
     if (g_lo + warp < ngroups) issue(g_lo + warp, 0);
@@ -546,7 +558,9 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
             float f = 1.f;
             if (sinks) ab_add_sink(sinks[head0 + r] * AB_LOG2E, M, L, f);
             if (gate_col >= 0) f *= ab_gate(q, q_row_stride, t, gate_col, head0 + r);
-            out[(size_t)t * out_row_stride + (size_t)(head0 + r) * DV + d] = __float2bfloat16_rn(acc * f / L);
+            const size_t at = (size_t)t * out_row_stride + (size_t)(head0 + r) * DV + d;
+            if (out_f32) reinterpret_cast<float*>(out)[at] = acc * f / L;
+            else out[at] = __float2bfloat16_rn(acc * f / L);
         } else {
             float* dst = scratch + (((size_t)t * H + head0 + r) * gridDim.z + blockIdx.z) * (DV + 2);
             dst[d] = acc;
@@ -558,7 +572,7 @@ biased_decode_kernel(const bf16* __restrict__ q, int q_row_stride, const bf16* _
 // The runs' parts of one (token, head), added in order: out = sum_z acc_z 2^(M_z - M) / sum_z L_z 2^(M_z - M).
 __global__ void biased_decode_join_kernel(const float* __restrict__ scratch, bf16* __restrict__ out, int out_row_stride,
                                           int H, int DV, int runs, const float* __restrict__ sinks,
-                                          const bf16* __restrict__ qrows, int q_row_stride, int gate_col) {
+                                          const bf16* __restrict__ qrows, int q_row_stride, int gate_col, int out_f32) {
     pdl_wait();
     pdl_trigger();
     const int t = blockIdx.x, h = blockIdx.y;
@@ -576,7 +590,9 @@ __global__ void biased_decode_join_kernel(const float* __restrict__ scratch, bf1
         float f = 1.f;
         if (sinks) ab_add_sink(sinks[h] * AB_LOG2E, M, L, f);
         if (gate_col >= 0) f *= ab_gate(qrows, q_row_stride, t, gate_col, h);
-        out[(size_t)t * out_row_stride + (size_t)h * DV + d] = __float2bfloat16_rn(acc * f / L);
+        const size_t at = (size_t)t * out_row_stride + (size_t)h * DV + d;
+        if (out_f32) reinterpret_cast<float*>(out)[at] = acc * f / L;
+        else out[at] = __float2bfloat16_rn(acc * f / L);
     }
 }
 
@@ -585,7 +601,7 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
                                 const int* block_table, int max_blocks, const int* seq_of_token, const int* positions,
                                 bf16* out, int out_row_stride, float scale, float bias_exp, int window, int keep_first,
                                 int tokens, int H, int Hk, int S, float* scratch, int runs, const float* sinks, int gate_col,
-                                float softcap, cudaStream_t stream) {
+                                float softcap, int v_share, int out_f32, cudaStream_t stream) {
     constexpr int KROW = ab_pow2(DK / 8) * 16, VROW = ab_pow2(DV / 8) * 16;
     const size_t walk = (size_t)AD_WARPS * 2 * (16 * KROW + 16 * VROW), parts = (size_t)AD_WARPS * 16 * (DV + 2) * 4;
     const size_t smem = 16 * KROW + (walk > parts ? walk : parts);
@@ -600,10 +616,10 @@ static int launch_biased_decode(const bf16* q, int q_row_stride, const bf16* k_p
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_decode_kernel<DK, DV>), grid, AD_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
                 v_pool, block_table, max_blocks, seq_of_token, positions, out, out_row_stride, scale * AB_LOG2E, bias_exp,
                 window, keep_first, H, Hk, S, share_log2, scratch, sinks, gate_col, softcap * AB_LOG2E,
-                softcap > 0.f ? scale / softcap : 0.f);
+                softcap > 0.f ? scale / softcap : 0.f, v_share, out_f32);
     if (runs > 1)
         VX_LAUNCH_K(VX_K_JOIN, biased_decode_join_kernel, dim3(tokens, H), DV >= 128 ? 128 : 64, 0, stream, (const float*)scratch,
-                    out, out_row_stride, H, DV, runs, sinks, q, q_row_stride, gate_col);
+                    out, out_row_stride, H, DV, runs, sinks, q, q_row_stride, gate_col, out_f32);
     VX_LAUNCH_CHECK();
     return VX_OK;
 }
@@ -612,7 +628,7 @@ template <int DK, int DV>
 static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, const bf16* v_pool, const int* block_table,
                          int max_blocks, AbSegments seg, bf16* out, int out_row_stride, float scale, float bias_exp,
                          int window, int keep_first, int segments, int max_new, int H, int Hk, int S, const float* sinks,
-                         int gate_col, float softcap, const AbLayout* layout, cudaStream_t stream) {
+                         int gate_col, float softcap, const AbLayout* layout, int v_share, int out_f32, cudaStream_t stream) {
     constexpr int KROW = ab_chunks(DK / 8) * 16, VROW = ab_chunks(DV / 8) * 16;
     const size_t smem = (size_t)AB_BM * KROW + 2 * ((size_t)AB_BN * KROW + (size_t)AB_BN * VROW);
     static bool configured[VX_MAX_DEVICES];
@@ -622,7 +638,8 @@ static int launch_biased(const bf16* q, int q_row_stride, const bf16* k_pool, co
     if (G > 1 && G <= 16 && (G & (G - 1)) == 0)
         while ((1 << share_log2) < G) ++share_log2;
     const int toks_per_tile = AB_BM >> share_log2;
-    AbLayout lay = {(long long)Hk * S * DK, (long long)S * DK, DK, (long long)Hk * S * DV, (long long)S * DV, DV, 0};
+    AbLayout lay = {(long long)Hk * S * DK, (long long)S * DK, DK, (long long)(Hk / v_share) * S * DV, (long long)S * DV, DV, 0,
+                    v_share, out_f32};
     if (layout) lay = *layout;
     dim3 grid((max_new + toks_per_tile - 1) / toks_per_tile, share_log2 ? Hk : H, segments);
     VX_LAUNCH_K(VX_K_ATTENTION, (biased_attention_kernel<DK, DV>), grid, AB_WARPS * 32, smem, stream, q, q_row_stride, k_pool,
@@ -642,13 +659,15 @@ static int biased_attention_any(const void* q, int q_row_stride, const void* k_p
                                        float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
                                        int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
                                        int gate_col, float softcap, const int* seq_list, const AbLayout* layout,
-                                       cudaStream_t stream) {
+                                       int v_share, int out_f32, cudaStream_t stream) {
     if (segments <= 0 || max_new <= 0) return VX_OK;
-    if (softcap < 0.f) return VX_ERR_SHAPE;
+    if (v_share <= 0) v_share = 1;
+    if (softcap < 0.f || Hk % v_share || (layout && v_share > 1)) return VX_ERR_SHAPE;
     if (H <= 0 || Hk <= 0 || H % Hk || S <= 0 || S % 16 || window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
     if (cu_seqlens ? !kv_offsets : (!seq_of_token || !positions || max_new != 1)) return VX_ERR_SHAPE;
     if (H > 65535 || segments > 65535) return VX_ERR_LIMIT;
-    if ((q_row_stride & 7) || (((uintptr_t)q) & 15) || (out_row_stride & 1) || (((uintptr_t)out) & 3)) return VX_ERR_ALIGN;
+    if ((q_row_stride & 7) || (((uintptr_t)q) & 15) || (out_row_stride & 1) || (((uintptr_t)out) & (out_f32 ? 7 : 3)))
+        return VX_ERR_ALIGN;
     if (layout && (!cu_seqlens || ((layout->k_page | layout->k_head | layout->k_row | layout->v_page | layout->v_head | layout->v_row) & 7) ||
                    (((uintptr_t)k_pool | (uintptr_t)v_pool) & 15)))
         return VX_ERR_ALIGN;
@@ -659,7 +678,7 @@ static int biased_attention_any(const void* q, int q_row_stride, const void* k_p
         return launch_biased_decode<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool,       \
                                             block_table, max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, \
                                             scale, bias_exp, window, keep_first, segments, H, Hk, S, scratch, runs, sinks,  \
-                                            gate_col, softcap, stream)
+                                            gate_col, softcap, v_share, out_f32, stream)
         AD_GO(64, 32); AD_GO(64, 64); AD_GO(64, 128); AD_GO(128, 32); AD_GO(128, 64); AD_GO(128, 128);
         AD_GO(32, 32); AD_GO(48, 48); AD_GO(80, 80); AD_GO(96, 96); AD_GO(112, 112);
 #undef AD_GO
@@ -670,12 +689,25 @@ static int biased_attention_any(const void* q, int q_row_stride, const void* k_p
     if (DK == K_ && DV == V_)                                                                                             \
         return launch_biased<K_, V_>((const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table, \
                                      max_blocks, seg, (bf16*)out, out_row_stride, scale, bias_exp, window, keep_first,    \
-                                     segments, max_new, H, Hk, S, sinks, gate_col, softcap, layout, stream)
+                                     segments, max_new, H, Hk, S, sinks, gate_col, softcap, layout, v_share, out_f32, stream)
     AB_GO(64, 32); AB_GO(64, 64); AB_GO(64, 128); AB_GO(128, 32); AB_GO(128, 64); AB_GO(128, 128);
     AB_GO(32, 32); AB_GO(48, 48); AB_GO(80, 80); AB_GO(96, 96); AB_GO(112, 112);
     AB_GO(192, 128); AB_GO(192, 64); AB_GO(96, 64); AB_GO(96, 32); AB_GO(256, 128);   // (portions only: no kernel for single tokens)
 #undef AB_GO
     return VX_ERR_SHAPE;
+}
+
+// `v_share` > 1: that many consecutive key heads read one value head (the value pool is [page, Hk / v_share, S, DV]);
+// `out_f32`: out is float32 [tokens, out_row_stride] whatever the inputs' type.
+extern "C" int vx_biased_attention_shared(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
+                                          const int* block_table, int max_blocks, const int* cu_seqlens, const int* kv_offsets,
+                                          const int* seq_of_token, const int* positions, void* out, int out_row_stride,
+                                          float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
+                                          int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
+                                          int gate_col, float softcap, int v_share, int out_f32, cudaStream_t stream) {
+    return biased_attention_any(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, cu_seqlens, kv_offsets, seq_of_token,
+                                positions, out, out_row_stride, scale, bias_exp, window, keep_first, segments, max_new, H, Hk,
+                                DK, DV, S, scratch, runs, sinks, gate_col, softcap, nullptr, nullptr, v_share, out_f32, stream);
 }
 
 extern "C" int vx_biased_attention_cap(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,
@@ -684,24 +716,36 @@ extern "C" int vx_biased_attention_cap(const void* q, int q_row_stride, const vo
                                        float scale, float bias_exp, int window, int keep_first, int segments, int max_new,
                                        int H, int Hk, int DK, int DV, int S, float* scratch, int runs, const float* sinks,
                                        int gate_col, float softcap, cudaStream_t stream) {
-    return biased_attention_any(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, cu_seqlens, kv_offsets, seq_of_token,
-                                positions, out, out_row_stride, scale, bias_exp, window, keep_first, segments, max_new, H, Hk,
-                                DK, DV, S, scratch, runs, sinks, gate_col, softcap, nullptr, nullptr, stream);
+    return vx_biased_attention_shared(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, cu_seqlens, kv_offsets,
+                                      seq_of_token, positions, out, out_row_stride, scale, bias_exp, window, keep_first, segments,
+                                      max_new, H, Hk, DK, DV, S, scratch, runs, sinks, gate_col, softcap, 1, 0, stream);
 }
 
 // Portions whose keys and values lie as rows that a matrix product left: key j of head hk of segment s at
 // k + (table[s][j / S] * S + j % S) * k_row + hk * k_head (values alike); segment s is request seq_list[s] (null: s) in
-// cu_seqlens and kv_offsets.  Causal, no window, no bias by distance, no sink or gate.
+// cu_seqlens and kv_offsets.  Causal, with a window > 0 only the last `window` positions up to a query's own (the table
+// then needs true entries only from the block of the first key that the segment's first query sees); no bias by
+// distance, no sink or gate.
+extern "C" int vx_biased_attention_rows_window(const void* q, int q_row_stride, const void* k, long long k_row, long long k_head,
+                                               const void* v, long long v_row, long long v_head, const int* block_table,
+                                               int max_blocks, const int* cu_seqlens, const int* kv_offsets, const int* seq_list,
+                                               void* out, int out_row_stride, float scale, int segments, int max_new, int H,
+                                               int Hk, int DK, int DV, int S, float softcap, int window, cudaStream_t stream) {
+    AbLayout lay = {k_row * S, k_head, k_row, v_row * S, v_head, v_row, 1, 1, 0};
+    if (k_row < DK || v_row < DV || window < 0) return VX_ERR_SHAPE;
+    return biased_attention_any(q, q_row_stride, k, v, block_table, max_blocks, cu_seqlens, kv_offsets, nullptr, nullptr, out,
+                                out_row_stride, scale, 0.f, window, 0, segments, max_new, H, Hk, DK, DV, S, nullptr, 1, nullptr, -1,
+                                softcap, seq_list, &lay, 1, 0, stream);
+}
+
 extern "C" int vx_biased_attention_rows(const void* q, int q_row_stride, const void* k, long long k_row, long long k_head,
                                         const void* v, long long v_row, long long v_head, const int* block_table,
                                         int max_blocks, const int* cu_seqlens, const int* kv_offsets, const int* seq_list,
                                         void* out, int out_row_stride, float scale, int segments, int max_new, int H, int Hk,
                                         int DK, int DV, int S, float softcap, cudaStream_t stream) {
-    AbLayout lay = {k_row * S, k_head, k_row, v_row * S, v_head, v_row, 1};
-    if (k_row < DK || v_row < DV) return VX_ERR_SHAPE;
-    return biased_attention_any(q, q_row_stride, k, v, block_table, max_blocks, cu_seqlens, kv_offsets, nullptr, nullptr, out,
-                                out_row_stride, scale, 0.f, 0, 0, segments, max_new, H, Hk, DK, DV, S, nullptr, 1, nullptr, -1,
-                                softcap, seq_list, &lay, stream);
+    return vx_biased_attention_rows_window(q, q_row_stride, k, k_row, k_head, v, v_row, v_head, block_table, max_blocks,
+                                           cu_seqlens, kv_offsets, seq_list, out, out_row_stride, scale, segments, max_new, H, Hk,
+                                           DK, DV, S, softcap, 0, stream);
 }
 
 extern "C" int vx_biased_attention(const void* q, int q_row_stride, const void* k_pool, const void* v_pool,

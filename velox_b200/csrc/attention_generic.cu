@@ -37,7 +37,7 @@ __global__ void paged_attention_generic_kernel(
     const T* __restrict__ v_pool, const int* __restrict__ block_table, int max_blocks,
     const int* __restrict__ seq_of_token, const int* __restrict__ positions, T* __restrict__ out,
     int out_row_stride, float scale, int window, int H, int Hk, int D, int S, int Dv, int keep_first,
-    float bias_exp, const float* __restrict__ sinks, int gate_col, float softcap, int v_stride) {
+    float bias_exp, const float* __restrict__ sinks, int gate_col, float softcap, int v_stride, int v_share, int out_f32) {
     pdl_wait();
     pdl_trigger();
     __shared__ float q_s[ATT_MAX_D];
@@ -76,6 +76,7 @@ __global__ void paged_attention_generic_kernel(
             const int page = bt[j / S];
             base = ((size_t)page * Hk + hk) * S + (j % S);
             const T* kp = k_pool + base * D;
+            if (v_share > 1) base = ((size_t)page * (Hk / v_share) + hk / v_share) * S + (j % S);
             float dot = 0.f;
             for (int d = 0; d < D; ++d) dot += q_s[d] * to_f32(kp[d]);
             s = dot * scale;
@@ -133,8 +134,40 @@ __global__ void paged_attention_generic_kernel(
     for (int d = threadIdx.x; d < Dv; d += blockDim.x) {
         float o = 0.f;
         for (int w = 0; w < ATT_WARPS; ++w) o += acc_s[w][d] * wgt[w];
-        out[(size_t)t * out_row_stride + (size_t)h * Dv + d] = from_f32<T>(o / L * gate);
+        if (out_f32) reinterpret_cast<float*>(out)[(size_t)t * out_row_stride + (size_t)h * Dv + d] = o / L * gate;
+        else out[(size_t)t * out_row_stride + (size_t)h * Dv + d] = from_f32<T>(o / L * gate);
     }
+}
+
+// `v_share` > 1: that many consecutive key heads read one value head (the value pool has Hk / v_share heads);
+// `out_f32`: the output is written as float32 whatever the element type of the inputs.
+extern "C" int vx_paged_attention_generic_shared(const void* q, int q_row_stride, const void* k_pool,
+                                                 const void* v_pool, const int* block_table, int max_blocks,
+                                                 const int* seq_of_token, const int* positions, void* out,
+                                                 int out_row_stride, float scale, int window, int tokens,
+                                                 int H, int Hk, int D, int S, int dtype, int Dv, int keep_first,
+                                                 float bias_exp, const float* sinks, int gate_col, float softcap,
+                                                 int v_stride, int v_share, int out_f32, cudaStream_t stream) {
+    if (tokens <= 0) return VX_OK;
+    if (Dv <= 0) Dv = D;
+    if (v_stride <= 0) v_stride = Dv;
+    if (v_share <= 0) v_share = 1;
+    if (Hk % v_share) return VX_ERR_SHAPE;
+    if (v_stride < Dv || softcap < 0.f) return VX_ERR_SHAPE;
+    if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || Dv > ATT_MAX_D || S <= 0 || max_blocks <= 0)
+        return VX_ERR_SHAPE;
+    if (window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
+    dim3 grid(tokens, H);
+    if (dtype == VX_F32)
+        VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<float>), grid, ATT_WARPS * 32, 0, stream, (const float*)q, q_row_stride, (const float*)k_pool, (const float*)v_pool, block_table,
+            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col, softcap, v_stride, v_share, out_f32);
+    else if (dtype == VX_BF16)
+        VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, (const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
+            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col, softcap, v_stride, v_share, out_f32);
+    else
+        return VX_ERR_DTYPE;
+    VX_LAUNCH_CHECK();
+    return VX_OK;
 }
 
 extern "C" int vx_paged_attention_generic_cap(const void* q, int q_row_stride, const void* k_pool,
@@ -144,24 +177,9 @@ extern "C" int vx_paged_attention_generic_cap(const void* q, int q_row_stride, c
                                               int H, int Hk, int D, int S, int dtype, int Dv, int keep_first,
                                               float bias_exp, const float* sinks, int gate_col, float softcap,
                                               int v_stride, cudaStream_t stream) {
-    if (tokens <= 0) return VX_OK;
-    if (Dv <= 0) Dv = D;
-    if (v_stride <= 0) v_stride = Dv;
-    if (v_stride < Dv || softcap < 0.f) return VX_ERR_SHAPE;
-    if (H <= 0 || Hk <= 0 || H % Hk || D <= 0 || D > ATT_MAX_D || Dv > ATT_MAX_D || S <= 0 || max_blocks <= 0)
-        return VX_ERR_SHAPE;
-    if (window < 0 || keep_first < 0 || bias_exp < 0.f) return VX_ERR_SHAPE;
-    dim3 grid(tokens, H);
-    if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<float>), grid, ATT_WARPS * 32, 0, stream, (const float*)q, q_row_stride, (const float*)k_pool, (const float*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (float*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col, softcap, v_stride);
-    else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ATTENTION, (paged_attention_generic_kernel<bf16>), grid, ATT_WARPS * 32, 0, stream, (const bf16*)q, q_row_stride, (const bf16*)k_pool, (const bf16*)v_pool, block_table,
-            max_blocks, seq_of_token, positions, (bf16*)out, out_row_stride, scale, window, H, Hk, D, S, Dv, keep_first, bias_exp, sinks, gate_col, softcap, v_stride);
-    else
-        return VX_ERR_DTYPE;
-    VX_LAUNCH_CHECK();
-    return VX_OK;
+    return vx_paged_attention_generic_shared(q, q_row_stride, k_pool, v_pool, block_table, max_blocks, seq_of_token, positions,
+                                             out, out_row_stride, scale, window, tokens, H, Hk, D, S, dtype, Dv, keep_first,
+                                             bias_exp, sinks, gate_col, softcap, v_stride, 1, 0, stream);
 }
 
 extern "C" int vx_paged_attention_generic(const void* q, int q_row_stride, const void* k_pool,

@@ -97,7 +97,8 @@ template <typename T, int NR4>
 __global__ void __launch_bounds__(AL_WARPS * 32)
 latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, const int* __restrict__ block_table,
                         int max_blocks, const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                        T* __restrict__ out, float* __restrict__ scratch, float scale, int H, int C, int R, int S, int runs) {
+                        T* __restrict__ out, float* __restrict__ scratch, float scale, int H, int C, int R, int S, int runs,
+                        int window) {
     extern __shared__ __align__(16) float al_smem[];
     const int W = C + R, Wp = (W + 3) & ~3, ld = al_row_stride(W);
     float* k_s = al_smem;                    // [AL_TILE][ld]
@@ -110,9 +111,13 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
     pdl_trigger();
     const int kv_len = positions[t] + 1;
     const int* bt = block_table + (size_t)seq_of_token[t] * max_blocks;
+    // with a window only the last `window` positions count: the tiles before the first of them are never touched (their
+    // pages may be gone), and in its tile the rows before it are staged as zeros and left out of the softmax
+    const int start = (window > 0 && kv_len > window) ? kv_len - window : 0;
+    const int first_tile = start / AL_TILE;
     const int tiles = (kv_len + AL_TILE - 1) / AL_TILE;
-    const int per_run = (tiles + runs - 1) / runs;
-    const int tile0 = run * per_run, tile1 = min(tiles, tile0 + per_run);
+    const int per_run = (tiles - first_tile + runs - 1) / runs;
+    const int tile0 = first_tile + run * per_run, tile1 = min(tiles, tile0 + per_run);
 
     {
         const T* src[AL_HEADS / AL_WARPS];
@@ -138,7 +143,8 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
     for (int tile = tile0; tile < tile1; ++tile) {
         const int j0 = tile * AL_TILE, n = min(AL_TILE, kv_len - j0);
         __syncthreads();   // the tile before this one has been used (and, the first time, the queries are written)
-        const int my_page = lane < n ? bt[(j0 + lane) / S] : 0;   // (one trip to the table for the tile's 32 rows)
+        const int lo = max(0, start - j0);   // rows of the tile before the window
+        const int my_page = (lane < n && lane >= lo) ? bt[(j0 + lane) / S] : 0;   // (one trip to the table for the tile's 32 rows)
 #pragma unroll
         for (int b = 0; b < AL_TILE / AL_WARPS; b += 4) {   // four rows of the warp's eight at a time
             const T* src[4];
@@ -146,7 +152,7 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
             for (int i = 0; i < 4; ++i) {
                 const int r = warp + (b + i) * AL_WARPS;
                 const int page = __shfl_sync(0xffffffffu, my_page, r);
-                src[i] = r < n ? pool + ((size_t)page * S + ((j0 + r) % S)) * W : nullptr;
+                src[i] = (r < n && r >= lo) ? pool + ((size_t)page * S + ((j0 + r) % S)) * W : nullptr;
             }
             al_stage_rows<4>(k_s + (warp + b * AL_WARPS) * ld, AL_WARPS * ld, src, W, Wp, lane);
         }
@@ -169,9 +175,10 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
         float p[AL_HW];
 #pragma unroll
         for (int hh = 0; hh < AL_HW; ++hh) {
-            const float s = lane < n ? dot[hh] * scale : -INFINITY;
+            const bool seen = lane < n && lane >= lo;
+            const float s = seen ? dot[hh] * scale : -INFINITY;
             const float m_new = fmaxf(m[hh], warp_max(s));
-            p[hh] = lane < n ? expf(s - m_new) : 0.f;
+            p[hh] = seen ? expf(s - m_new) : 0.f;
             const float alpha = expf(m[hh] - m_new);   // m = -inf before the first tile: 0
             l[hh] = l[hh] * alpha + warp_sum(p[hh]);
 #pragma unroll
@@ -184,7 +191,7 @@ latent_attention_kernel(const T* __restrict__ qa, const T* __restrict__ pool, co
         *reinterpret_cast<float4*>(pw + lane * AL_HW) = make_float4(p[0], p[1], p[2], p[3]);
         __syncwarp();
 #pragma unroll 2
-        for (int jj = 0; jj < n; ++jj) {
+        for (int jj = lo; jj < n; ++jj) {
             const float4 p4 = *reinterpret_cast<const float4*>(pw + jj * AL_HW);
             const float pj[AL_HW] = {p4.x, p4.y, p4.z, p4.w};
             const float* vr = k_s + jj * ld;
@@ -267,7 +274,7 @@ __global__ void latent_attention_join_kernel(const float* __restrict__ scratch, 
 template <typename T>
 static int launch_latent_attention(const T* qa, const T* pool, const int* block_table, int max_blocks, const int* seq_of_token,
                                    const int* positions, T* out, float* scratch, float scale, int tokens, int H, int C, int R,
-                                   int S, int runs, cudaStream_t stream) {
+                                   int S, int runs, int window, cudaStream_t stream) {
     const int W = C + R, Wp = (W + 3) & ~3;
     const size_t smem = sizeof(float) * ((size_t)AL_TILE * al_row_stride(W) + (size_t)AL_HEADS * Wp + AL_WARPS * AL_TILE * AL_HW);
     const size_t smem_max = sizeof(float) * ((size_t)AL_TILE * al_row_stride(1024) + (size_t)AL_HEADS * 1024 + AL_WARPS * AL_TILE * AL_HW);
@@ -277,7 +284,7 @@ static int launch_latent_attention(const T* qa, const T* pool, const int* block_
     do {                                                                                                              \
         if (int rc = vx_configure_smem(latent_attention_kernel<T, NR4>, smem_max, configured[SLOT])) return rc;        \
         VX_LAUNCH_K(VX_K_ATTENTION, (latent_attention_kernel<T, NR4>), grid, AL_WARPS * 32, smem, stream, qa, pool,    \
-                    block_table, max_blocks, seq_of_token, positions, out, scratch, scale, H, C, R, S, runs);          \
+                    block_table, max_blocks, seq_of_token, positions, out, scratch, scale, H, C, R, S, runs, window);  \
     } while (0)
     if (C <= 128) AL_GO(1, 0);
     else if (C <= 256) AL_GO(2, 1);
@@ -292,43 +299,56 @@ static int launch_latent_attention(const T* qa, const T* pool, const int* block_
 }
 
 // qa [tokens, H, C + R] folded queries; pool [pages, 1, S, C + R]; token row t is request seq_of_token[t] at position
-// positions[t] and sees positions 0 .. positions[t].  out [tokens, H, C].  scratch: float32, tokens * H * runs * (C + 2)
-// elements, needed for runs > 1.
-extern "C" int vx_latent_attention(const void* qa, const void* pool, const int* block_table, int max_blocks,
-                                   const int* seq_of_token, const int* positions, void* out, float* scratch, float scale,
-                                   int tokens, int H, int C, int R, int S, int runs, int dtype, cudaStream_t stream) {
+// positions[t] and sees positions 0 .. positions[t], with a window > 0 only the last `window` of them.  out [tokens, H, C].
+// scratch: float32, tokens * H * runs * (C + 2) elements, needed for runs > 1.
+extern "C" int vx_latent_attention_window(const void* qa, const void* pool, const int* block_table, int max_blocks,
+                                          const int* seq_of_token, const int* positions, void* out, float* scratch, float scale,
+                                          int tokens, int H, int C, int R, int S, int runs, int window, int dtype,
+                                          cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
+    if (window < 0) return VX_ERR_SHAPE;
     if (H <= 0 || C <= 0 || R < 0 || S <= 0 || max_blocks <= 0 || C + R > 1024 || runs < 1 || runs > AL_MAX_RUNS) return VX_ERR_SHAPE;
     if (runs > 1 && !scratch) return VX_ERR_SHAPE;
     if ((H + AL_HEADS - 1) / AL_HEADS > 65535 || runs > 65535) return VX_ERR_LIMIT;
     if (dtype == VX_F32)
         return launch_latent_attention<float>((const float*)qa, (const float*)pool, block_table, max_blocks, seq_of_token,
-                                              positions, (float*)out, scratch, scale, tokens, H, C, R, S, runs, stream);
+                                              positions, (float*)out, scratch, scale, tokens, H, C, R, S, runs, window, stream);
     if (dtype == VX_BF16)
         return launch_latent_attention<bf16>((const bf16*)qa, (const bf16*)pool, block_table, max_blocks, seq_of_token,
-                                             positions, (bf16*)out, scratch, scale, tokens, H, C, R, S, runs, stream);
+                                             positions, (bf16*)out, scratch, scale, tokens, H, C, R, S, runs, window, stream);
     return VX_ERR_DTYPE;
+}
+
+extern "C" int vx_latent_attention(const void* qa, const void* pool, const int* block_table, int max_blocks,
+                                   const int* seq_of_token, const int* positions, void* out, float* scratch, float scale,
+                                   int tokens, int H, int C, int R, int S, int runs, int dtype, cudaStream_t stream) {
+    return vx_latent_attention_window(qa, pool, block_table, max_blocks, seq_of_token, positions, out, scratch, scale, tokens,
+                                      H, C, R, S, runs, 0, dtype, stream);
 }
 
 // The cached rows of the segments of a step, gathered page by page into one matrix: segment s (request seq_list[s], or
 // s) holds positions 0 .. kv_offsets + new tokens - 1; its rows start at row table[s][0] * S_out of `rows` and are filled
-// with zeros up to the next multiple of S_out.  grid (run of 32 rows, segment); 8 warps, a warp per row.
+// with zeros up to the next multiple of S_out.  With a window > 0 only the positions from
+// first = floor(max(0, kv_offsets + 1 - window), S_out) on are copied (what the segment's first query sees, from a block's
+// start), position j to row table[s][0] * S_out + j - first.  grid (run of 32 rows, segment); 8 warps, a warp per row.
 template <typename T>
 __global__ void latent_gather_kernel(const T* __restrict__ pool, const int* __restrict__ block_table, int max_blocks,
                                      const int* __restrict__ cu_seqlens, const int* __restrict__ kv_offsets,
                                      const int* __restrict__ seq_list, const int* __restrict__ out_table, int out_blocks,
-                                     T* __restrict__ rows, int W, int S, int S_out) {
+                                     T* __restrict__ rows, int W, int S, int S_out, int window) {
     pdl_wait();
     pdl_trigger();
     const int s = blockIdx.y, seq = seq_list ? seq_list[s] : s;
     const int kv_len = kv_offsets[seq] + cu_seqlens[seq + 1] - cu_seqlens[seq];
+    const int seen_from = window > 0 ? max(0, kv_offsets[seq] + 1 - window) : 0;
+    const int first = seen_from / S_out * S_out;
     const int padded = (kv_len + S_out - 1) / S_out * S_out;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* bt = block_table + (size_t)seq * max_blocks;
     const size_t base = (size_t)out_table[(size_t)s * out_blocks] * S_out;
-    for (int j = blockIdx.x * 32 + warp; j < min(padded, blockIdx.x * 32 + 32); j += 8) {
-        T* dst = rows + (base + j) * W;
-        if (j < kv_len) {
+    for (int j = first + blockIdx.x * 32 + warp; j < min(padded, first + blockIdx.x * 32 + 32); j += 8) {
+        T* dst = rows + (base + j - first) * W;
+        if (j < kv_len && j >= seen_from) {   // (a position before the window may lie in a page that was given back)
             const T* src = pool + ((size_t)bt[j / S] * S + (j % S)) * W;
             for (int d = lane; d < W; d += 32) dst[d] = src[d];
         } else {
@@ -338,23 +358,32 @@ __global__ void latent_gather_kernel(const T* __restrict__ pool, const int* __re
 }
 
 // pool [pages, 1, S, W]; out_table int32 [segments, out_blocks]: the blocks of S_out rows that segment s takes in `rows`
-// (consecutive, the first one listed first); max_kv bounds any segment's positions after the step.
-extern "C" int vx_latent_gather(const void* pool, const int* block_table, int max_blocks, const int* cu_seqlens,
-                                const int* kv_offsets, const int* seq_list, const int* out_table, int out_blocks, void* rows,
-                                int segments, int max_kv, int W, int S, int S_out, int dtype, cudaStream_t stream) {
+// (consecutive, the first one listed first); max_kv bounds the rows that any segment takes (its positions after the step,
+// less the ones before its window's first block).
+extern "C" int vx_latent_gather_window(const void* pool, const int* block_table, int max_blocks, const int* cu_seqlens,
+                                       const int* kv_offsets, const int* seq_list, const int* out_table, int out_blocks, void* rows,
+                                       int segments, int max_kv, int W, int S, int S_out, int window, int dtype,
+                                       cudaStream_t stream) {
     if (segments <= 0 || max_kv <= 0) return VX_OK;
-    if (W <= 0 || S <= 0 || S_out <= 0 || max_blocks <= 0 || out_blocks <= 0) return VX_ERR_SHAPE;
+    if (W <= 0 || S <= 0 || S_out <= 0 || max_blocks <= 0 || out_blocks <= 0 || window < 0) return VX_ERR_SHAPE;
     if (segments > 65535) return VX_ERR_LIMIT;
     const int padded = (max_kv + S_out - 1) / S_out * S_out;
     dim3 grid((padded + 31) / 32, segments);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (latent_gather_kernel<float>), grid, 256, 0, stream, (const float*)pool, block_table,
-                    max_blocks, cu_seqlens, kv_offsets, seq_list, out_table, out_blocks, (float*)rows, W, S, S_out);
+                    max_blocks, cu_seqlens, kv_offsets, seq_list, out_table, out_blocks, (float*)rows, W, S, S_out, window);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (latent_gather_kernel<bf16>), grid, 256, 0, stream, (const bf16*)pool, block_table,
-                    max_blocks, cu_seqlens, kv_offsets, seq_list, out_table, out_blocks, (bf16*)rows, W, S, S_out);
+                    max_blocks, cu_seqlens, kv_offsets, seq_list, out_table, out_blocks, (bf16*)rows, W, S, S_out, window);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
     return VX_OK;
+}
+
+extern "C" int vx_latent_gather(const void* pool, const int* block_table, int max_blocks, const int* cu_seqlens,
+                                const int* kv_offsets, const int* seq_list, const int* out_table, int out_blocks, void* rows,
+                                int segments, int max_kv, int W, int S, int S_out, int dtype, cudaStream_t stream) {
+    return vx_latent_gather_window(pool, block_table, max_blocks, cu_seqlens, kv_offsets, seq_list, out_table, out_blocks, rows,
+                                   segments, max_kv, W, S, S_out, 0, dtype, stream);
 }

@@ -224,11 +224,11 @@ extern "C" int vx_add_rmsnorm(const float* residual_in, const void* delta, const
 // Plain RMSNorm of rows of element type T (no residual), statistics in float32.
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ weight,
-                               T* __restrict__ out, int width, float eps) {
+                               T* __restrict__ out, int width, float eps, int ldx) {
     pdl_wait();
     pdl_trigger();
     __shared__ float scratch[32];
-    const T* xin = x + (size_t)blockIdx.x * width;
+    const T* xin = x + (size_t)blockIdx.x * ldx;
     T* o = out + (size_t)blockIdx.x * width;
     float ss = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
@@ -241,19 +241,25 @@ __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict_
         o[i] = from_f32<T>(to_f32(xin[i]) * rstd * weight[i]);
 }
 
-extern "C" int vx_rmsnorm(const void* x, const float* weight, void* out, int rows, int width,
-                          float eps, int dtype, cudaStream_t stream) {
+// Rows of `width` elements that start every `ldx` elements of x; out is [rows, width].
+extern "C" int vx_rmsnorm_rows(const void* x, int ldx, const float* weight, void* out, int rows, int width,
+                               float eps, int dtype, cudaStream_t stream) {
     if (rows <= 0) return VX_OK;
-    if (width <= 0) return VX_ERR_SHAPE;
+    if (width <= 0 || ldx < width) return VX_ERR_SHAPE;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (dtype == VX_F32)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (rmsnorm_kernel<float>), rows, threads, 0, stream, (const float*)x, weight, (float*)out, width, eps);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (rmsnorm_kernel<float>), rows, threads, 0, stream, (const float*)x, weight, (float*)out, width, eps, ldx);
     else if (dtype == VX_BF16)
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (rmsnorm_kernel<bf16>), rows, threads, 0, stream, (const bf16*)x, weight, (bf16*)out, width, eps);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (rmsnorm_kernel<bf16>), rows, threads, 0, stream, (const bf16*)x, weight, (bf16*)out, width, eps, ldx);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
     return VX_OK;
+}
+
+extern "C" int vx_rmsnorm(const void* x, const float* weight, void* out, int rows, int width,
+                          float eps, int dtype, cudaStream_t stream) {
+    return vx_rmsnorm_rows(x, width, weight, out, rows, width, eps, dtype, stream);
 }
 
 // out[t, i] = act(gate) * up, activation and product in float32.  Where gate i

@@ -112,6 +112,18 @@ def _declare(lib) -> None:
         "vx_capped_gated_act": [P, P, P, I, I, F, F, I, P],
         "vx_sum_add_rmsnorm": [P, P, F, P, F, P, F, P, P, P, P, I, I, F, I, P],
         "vx_softcap_rows": [P, P, c_longlong, F, P],
+        "vx_qk_norm_rope_kv_shared": [P, I, P, P, F, P, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P],
+        "vx_paged_attention_generic_shared": [P, I, P, P, P, I, P, P, P, I, F, I, I, I, I, I, I, I, I, I, F, P, I, F, I, I, I, P],
+        "vx_latent_attention_window": [P, P, P, I, P, P, P, P, F, I, I, I, I, I, I, I, I, P],
+        "vx_stream_norm": [P, I, P, P, P, P, F, P, I, P, I, I, I, I, P],
+        "vx_stream_update": [P, I, P, P, F, P, P, I, P, P, F, P, I, I, I, I, P],
+        "vx_diff_combine": [P, I, P, I, I, P, F, F, F, I, I, I, I, I, P],
+        "vx_sigmoid_gate": [P, I, P, I, P, I, I, I, I, P],
+        "vx_rmsnorm_rows": [P, I, P, P, I, I, F, I, P],
+        "vx_biased_attention_shared": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P, I, P, I, F, I, I, P],
+        "vx_biased_attention_rows_window": [P, I, P, c_longlong, c_longlong, P, c_longlong, c_longlong, P, I, P, P, P, P, I, F, I, I,
+                                            I, I, I, I, I, F, I, P],
+        "vx_latent_gather_window": [P, P, I, P, P, P, P, I, P, I, I, I, I, I, I, I, P],
     }
     lib.vx_set_pdl_mask.argtypes = [I]
     lib.vx_set_pdl_mask.restype = None
@@ -235,13 +247,16 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMS norm of the rows of x times `weight`; a matrix whose rows are contiguous may be a slice of wider rows."""
     _dev(x, weight)
-    _need(x.is_contiguous() and weight.dtype == torch.float32, "rmsnorm: contiguous input, float32 weight")
     width = x.shape[-1]
+    _need(weight.dtype == torch.float32 and (x.is_contiguous() or (x.dim() == 2 and x.stride(1) == 1)),
+          "rmsnorm: contiguous rows, float32 weight")
     _need(weight.numel() == width, "rmsnorm: weight has %d elements, rows %d" % (weight.numel(), width))
-    out = torch.empty_like(x)
-    _check(library().vx_rmsnorm(_ptr(x), _ptr(weight), _ptr(out), x.numel() // width, width, float(eps),
-                                dtype_code(x.dtype), _stream()), "rmsnorm")
+    out = torch.empty(tuple(x.shape), dtype=x.dtype, device=x.device)
+    ldx = width if x.is_contiguous() else x.stride(0)
+    _check(library().vx_rmsnorm_rows(_ptr(x), ldx, _ptr(weight), _ptr(out), x.numel() // width, width, float(eps),
+                                     dtype_code(x.dtype), _stream()), "rmsnorm")
     return out
 
 
@@ -262,12 +277,15 @@ def gated_act(gate_up: torch.Tensor, activation: str, block: int = 0,
 
 def qk_norm_rope_kv(qkv: torch.Tensor, q_weight, k_weight, eps: float, inv_freq, rot_dim: int,
                     positions: torch.Tensor, slot_mapping, k_pool, v_pool, num_heads: int, num_kv_heads: int,
-                    head_dim: int, v_head_dim: int = 0, interleaved: bool = False) -> None:
-    """In place on the packed projections `qkv` [T, (H+Hk)D + Hk Dv (+ more)]; writes new keys
-    and values into the pools [pages, Hk, S, D] and [pages, Hk, S, Dv] when a slot mapping is given
-    (`v_head_dim` 0: values of the keys' size).  The rotation pairs channel i with i + rot_dim/2, or, when
-    `interleaved`, channel 2i with 2i + 1."""
+                    head_dim: int, v_head_dim: int = 0, interleaved: bool = False, num_v_heads: int = 0,
+                    magnitude: float = 1.0) -> None:
+    """In place on the packed projections `qkv` [T, (H+Hk)D + Hv Dv (+ more)]; writes new keys
+    and values into the pools [pages, Hk, S, D] and [pages, Hv, S, Dv] when a slot mapping is given
+    (`v_head_dim` 0: values of the keys' size; `num_v_heads` 0: as many value heads as key heads).  The rotation pairs
+    channel i with i + rot_dim/2, or, when `interleaved`, channel 2i with 2i + 1; cosines and sines are multiplied by
+    `magnitude`."""
     v_head_dim = int(v_head_dim) or head_dim
+    num_v_heads = int(num_v_heads) or num_kv_heads
     _dev(qkv, q_weight, k_weight, inv_freq, positions, slot_mapping, k_pool, v_pool)
     _need(qkv.is_contiguous() and positions.dtype == torch.int32, "qk_norm_rope_kv: contiguous qkv, int32 positions")
     page_size = 1
@@ -275,17 +293,18 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_weight, k_weight, eps: float, inv_freq,
         _need(k_pool is not None and v_pool is not None and k_pool.dtype == qkv.dtype and k_pool.is_contiguous()
               and v_pool.is_contiguous(), "qk_norm_rope_kv: pools of the activations' element type")
         _need(tuple(k_pool.shape[1:]) == (num_kv_heads, k_pool.shape[2], head_dim)
-              and tuple(v_pool.shape[1:]) == (num_kv_heads, k_pool.shape[2], v_head_dim), "qk_norm_rope_kv: pool shape")
+              and tuple(v_pool.shape[1:]) == (num_v_heads, k_pool.shape[2], v_head_dim), "qk_norm_rope_kv: pool shape")
         page_size = k_pool.shape[2]
     if inv_freq is not None:
         _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dim, "qk_norm_rope_kv: inv_freq size")
     for w in (q_weight, k_weight):
         if w is not None:
             _need(w.dtype == torch.float32 and w.numel() == head_dim, "qk_norm_rope_kv: norm weight size")
-    _check(library().vx_qk_norm_rope_kv_pairs(
+    _check(library().vx_qk_norm_rope_kv_shared(
         _ptr(qkv), qkv.shape[-1], _ptr(q_weight), _ptr(k_weight), float(eps), _ptr(inv_freq), int(rot_dim),
         _ptr(positions), _ptr(slot_mapping), _ptr(k_pool), _ptr(v_pool), qkv.shape[0], num_heads, num_kv_heads,
-        head_dim, page_size, dtype_code(qkv.dtype), v_head_dim, 1 if interleaved else 0, _stream()), "qk_norm_rope_kv")
+        head_dim, page_size, dtype_code(qkv.dtype), v_head_dim, 1 if interleaved else 0, num_v_heads, float(magnitude),
+        _stream()), "qk_norm_rope_kv")
 
 
 ATTENTION_MAX_HEAD_DIM = 256
@@ -301,14 +320,18 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
                             seq_of_token, positions, scale: float, window: int, num_heads: int,
                             num_kv_heads: int, head_dim: int, tokens: int, v_head_dim: int = 0, keep_first: int = 0,
                             bias_exponent: float = 0.0, sinks: Optional[torch.Tensor] = None,
-                            gate_col: int = -1, softcap: float = 0.0, v_stride: int = 0) -> torch.Tensor:
+                            gate_col: int = -1, softcap: float = 0.0, v_stride: int = 0, v_share: int = 1,
+                            out_float32: bool = False) -> torch.Tensor:
     """The general kernel.  `v_head_dim`: size of a value (0: a key's); `keep_first`: with a window, the
     first positions that stay visible; `bias_exponent` b > 0: head h's scores lose
     2^(-b (h + 1) / heads) * distance; `sinks` (float32 per head): the softmax's denominator also holds
     exp(sink); `gate_col` >= 0: head h's output times sigmoid of column gate_col + h of the token's row of `q`;
     `softcap` c > 0: a scaled score s becomes c tanh(s / c); `v_stride`: elements from one value row of
-    `v_pool` to the next (0: v_head_dim), for a pool whose rows hold the value inside the key's row."""
+    `v_pool` to the next (0: v_head_dim), for a pool whose rows hold the value inside the key's row; `v_share` > 1: that
+    many consecutive key heads read one value head (the value pool has num_kv_heads / v_share heads); `out_float32`: the
+    result is float32 whatever the queries' element type."""
     _dev(q, k_pool, v_pool, block_table, seq_of_token, positions, sinks)
+    _need(v_share >= 1 and num_kv_heads % v_share == 0, "paged_attention: v_share must divide the key heads")
     _check_sinks_gate("paged_attention", sinks, gate_col, num_heads, q_row_stride)
     v_head_dim = int(v_head_dim) or head_dim
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.dim() == 2,
@@ -318,12 +341,13 @@ def paged_attention_generic(q: torch.Tensor, q_row_stride: int, k_pool, v_pool, 
     _need(0 < head_dim <= ATTENTION_MAX_HEAD_DIM and 0 < v_head_dim <= ATTENTION_MAX_HEAD_DIM,
           "paged_attention: head sizes %d / %d (the general kernel takes sizes up to %d)"
           % (head_dim, v_head_dim, ATTENTION_MAX_HEAD_DIM))
-    out = torch.empty((tokens, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
-    _check(library().vx_paged_attention_generic_cap(
+    out = torch.empty((tokens, num_heads * v_head_dim), dtype=torch.float32 if out_float32 else q.dtype, device=q.device)
+    _check(library().vx_paged_attention_generic_shared(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1],
         _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale), int(window), tokens,
         num_heads, num_kv_heads, head_dim, page_size, dtype_code(q.dtype), v_head_dim, int(keep_first),
-        float(bias_exponent), _ptr(sinks), int(gate_col), float(softcap), int(v_stride), _stream()), "paged_attention_generic")
+        float(bias_exponent), _ptr(sinks), int(gate_col), float(softcap), int(v_stride), int(v_share),
+        1 if out_float32 else 0, _stream()), "paged_attention_generic")
     return out
 
 
@@ -351,8 +375,10 @@ def biased_attention_supported(dtype, head_dim: int, v_head_dim: int, page_size:
 
 def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions,
                       scale, window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, segments,
-                      max_new, tokens, out, max_kv=0, sinks=None, gate_col=-1, softcap=0.0):
+                      max_new, tokens, out, max_kv=0, sinks=None, gate_col=-1, softcap=0.0, v_share=1, out_float32=False):
     _dev(q, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, seq_of_token, positions, out, sinks)
+    _need(v_share >= 1 and num_kv_heads % v_share == 0 and v_pool.shape[1] * v_share == k_pool.shape[1] == num_kv_heads,
+          "biased_attention: value heads times v_share must be the key heads")
     _check_sinks_gate("biased_attention", sinks, gate_col, num_heads, q_row_stride)
     _need(q.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16 and v_pool.dtype == torch.bfloat16,
           "biased_attention: bfloat16 only")
@@ -361,7 +387,8 @@ def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, 
     _need(k_pool.is_contiguous() and v_pool.is_contiguous() and k_pool.shape[3] == head_dim and v_pool.shape[3] == v_head_dim,
           "biased_attention: pools [pages, kv heads, page size, head size]")
     if out is None:
-        out = torch.empty((tokens, num_heads * v_head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((tokens, num_heads * v_head_dim), dtype=torch.float32 if out_float32 else q.dtype, device=q.device)
+    _need(out.dtype == (torch.float32 if out_float32 else q.dtype), "biased_attention: the output's element type")
     # single tokens with many visible keys: the keys cut into runs of at least 16 groups of 16, 8 runs at most
     runs, scratch = 1, None
     if cu_seqlens is None and max_kv > 0:
@@ -369,38 +396,40 @@ def _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, 
         runs = max(1, min(BIASED_DECODE_MAX_RUNS, -(-keys // 16) // 16))
         if runs > 1:
             scratch = workspace(q.device, tokens * num_heads * runs * (v_head_dim + 2), which="biased_decode")
-    _check(library().vx_biased_attention_cap(
+    _check(library().vx_biased_attention_shared(
         _ptr(q), q_row_stride, _ptr(k_pool), _ptr(v_pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens),
         _ptr(kv_offsets), _ptr(seq_of_token), _ptr(positions), _ptr(out), num_heads * v_head_dim, float(scale),
         float(bias_exponent), int(window), int(keep_first), int(segments), int(max_new), num_heads, num_kv_heads, head_dim,
-        v_head_dim, k_pool.shape[2], _ptr(scratch), runs, _ptr(sinks), int(gate_col), float(softcap), _stream()),
-        "biased_attention")
+        v_head_dim, k_pool.shape[2], _ptr(scratch), runs, _ptr(sinks), int(gate_col), float(softcap), int(v_share),
+        1 if out_float32 else 0, _stream()), "biased_attention")
     return out
 
 
 def biased_prefill_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, scale: float,
                              window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
                              head_dim: int, v_head_dim: int, requests: int, max_new: int, tokens: int, out=None,
-                             sinks=None, gate_col: int = -1, softcap: float = 0.0):
+                             sinks=None, gate_col: int = -1, softcap: float = 0.0, v_share: int = 1, out_float32: bool = False):
     """Attention of prompt portions (request i: rows cu_seqlens[i] .. at positions kv_offsets[i] ..) with
     score = q.k * scale - 2^(-bias_exponent (h+1) / heads) * distance under a window that keeps the first
     `keep_first` positions; bfloat16, tensor cores, probabilities in two bfloat16 halves.  `sinks`, `gate_col` and
-    `softcap` as in `paged_attention_generic`."""
+    `softcap`, `v_share` and `out_float32` as in `paged_attention_generic`."""
     return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, cu_seqlens, kv_offsets, None, None, scale,
                              window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, requests,
-                             max_new, tokens, out, sinks=sinks, gate_col=gate_col, softcap=softcap)
+                             max_new, tokens, out, sinks=sinks, gate_col=gate_col, softcap=softcap, v_share=v_share,
+                             out_float32=out_float32)
 
 
 def biased_decode_attention(q, q_row_stride, k_pool, v_pool, block_table, seq_of_token, positions, scale: float,
                             window: int, keep_first: int, bias_exponent: float, num_heads: int, num_kv_heads: int,
                             head_dim: int, v_head_dim: int, tokens: int, out=None, max_kv: int = 0, sinks=None,
-                            gate_col: int = -1, softcap: float = 0.0):
+                            gate_col: int = -1, softcap: float = 0.0, v_share: int = 1, out_float32: bool = False):
     """The same for token rows that each stand alone: row t is request seq_of_token[t] at position positions[t].
     `max_kv` (a bound on any row's position + 1; 0: unknown) lets rows with many visible keys be cut into runs that
     several blocks share."""
     return _biased_attention(q, q_row_stride, k_pool, v_pool, block_table, None, None, seq_of_token, positions, scale,
                              window, keep_first, bias_exponent, num_heads, num_kv_heads, head_dim, v_head_dim, tokens, 1,
-                             tokens, out, max_kv=max_kv, sinks=sinks, gate_col=gate_col, softcap=softcap)
+                             tokens, out, max_kv=max_kv, sinks=sinks, gate_col=gate_col, softcap=softcap, v_share=v_share,
+                             out_float32=out_float32)
 
 
 def embedding_pair(ids, positions, seq_of_token, cu_seqlens, state_slots, last_token: torch.Tensor,
@@ -991,14 +1020,16 @@ def latent_prep(down: torch.Tensor, q: torch.Tensor, qa: Optional[torch.Tensor],
     _dev(down, q, qa, weight, inv_freq, positions, slot_mapping, pool)
     _need(qa is None or (qa.is_contiguous() and qa.dtype == q.dtype and tuple(qa.shape) == (q.shape[0], heads, rank + rot_dim)),
           "latent_prep: folded queries [T, heads, rank + rot_dim]")
-    _need(down.stride(1) == 1 and q.stride(1) == 1 and down.dtype == q.dtype and positions.dtype == torch.int32,
+    _need((down is None or (down.stride(1) == 1 and down.dtype == q.dtype)) and q.stride(1) == 1 and positions.dtype == torch.int32,
           "latent_prep: rows contiguous, one element type, int32 positions")
-    _need(weight.dtype == torch.float32 and weight.numel() == rank and inv_freq.dtype == torch.float32
-          and inv_freq.numel() * 2 == rot_dim, "latent_prep: float32 weight [rank] and rot_dim / 2 frequencies")
+    _need(down is not None or slot_mapping is None, "latent_prep: a row to write needs the projection that made it")
+    _need((weight is None and down is None) or (weight is not None and weight.dtype == torch.float32 and weight.numel() == rank),
+          "latent_prep: float32 weight [rank] for the row that the projection made")
+    _need(inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == rot_dim, "latent_prep: rot_dim / 2 frequencies")
     if slot_mapping is not None:
         _need(pool is not None and pool.dtype == q.dtype and pool.is_contiguous() and pool.shape[-1] == rank + rot_dim,
               "latent_prep: a pool of rows of rank + rot_dim elements")
-    _check(library().vx_latent_prep(_ptr(down), down.stride(0), _ptr(q), q.stride(0), _ptr(qa), _ptr(weight), float(eps), _ptr(inv_freq),
+    _check(library().vx_latent_prep(_ptr(down), down.stride(0) if down is not None else 0, _ptr(q), q.stride(0), _ptr(qa), _ptr(weight), float(eps), _ptr(inv_freq),
                                     1 if interleaved else 0, _ptr(positions), _ptr(slot_mapping), _ptr(pool), q.shape[0],
                                     heads, dim, rot_dim, rank, dtype_code(q.dtype), _stream()), "latent_prep")
 
@@ -1009,14 +1040,16 @@ LATENT_ATTENTION_BLOCK_HEADS = 16   # query heads that share a staged tile of ro
 
 
 def latent_attention(qa: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor, seq_of_token, positions, scale: float,
-                     heads: int, rank: int, rot_dim: int, max_kv: int = 0) -> torch.Tensor:
+                     heads: int, rank: int, rot_dim: int, max_kv: int = 0, window: int = 0) -> torch.Tensor:
     """Causal softmax attention of folded queries qa [tokens, heads, rank + rot_dim] over cached latent rows
     (`pool` [pages, 1, page size, rank + rot_dim]; token row t is request seq_of_token[t] at position positions[t]):
     score = qa . row * scale, the value is a row's first `rank` elements.  Returns [tokens, heads, rank] in qa's element
     type.  `max_kv` (a bound on any row's position + 1; 0: unknown) lets a step of few rows cut their keys into runs
-    that several blocks share."""
+    that several blocks share.  With `window` > 0 a row sees only the last `window` positions up to its own."""
     _dev(qa, pool, block_table, seq_of_token, positions)
     tokens, width = qa.shape[0], rank + rot_dim
+    if window > 0 and max_kv > 0:
+        max_kv = min(max_kv, int(window) + 31)   # (what a row reads at most: its window, from a tile's start)
     _need(qa.is_contiguous() and tuple(qa.shape) == (tokens, heads, width) and pool.dtype == qa.dtype and pool.is_contiguous()
           and pool.dim() == 4 and pool.shape[1] == 1 and pool.shape[3] == width,
           "latent_attention: folded queries [T, heads, rank + rot_dim] and a pool of rows of that width")
@@ -1030,9 +1063,10 @@ def latent_attention(qa: torch.Tensor, pool: torch.Tensor, block_table: torch.Te
         if runs > 1:
             scratch = workspace(qa.device, tokens * heads * runs * (rank + 2), which="latent_attention")
     out = torch.empty((tokens, heads, rank), dtype=qa.dtype, device=qa.device)
-    _check(library().vx_latent_attention(_ptr(qa), _ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
-                                         _ptr(positions), _ptr(out), _ptr(scratch), float(scale), tokens, heads, rank, rot_dim,
-                                         pool.shape[2], runs, dtype_code(qa.dtype), _stream()), "latent_attention")
+    _check(library().vx_latent_attention_window(_ptr(qa), _ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(seq_of_token),
+                                                _ptr(positions), _ptr(out), _ptr(scratch), float(scale), tokens, heads, rank,
+                                                rot_dim, pool.shape[2], runs, int(window), dtype_code(qa.dtype), _stream()),
+           "latent_attention")
     return out
 
 
@@ -1041,31 +1075,40 @@ RAISED_ROWS_BLOCK = 64   # rows of keys and values raised for a step lie in bloc
 
 class RaisedPlan:
     """Where the raised keys and values of a step's requests lie: request i (holding `kv_lens[i]` positions after the step)
-    takes the rows `first[i] * RAISED_ROWS_BLOCK` onward of a matrix of `rows` rows; `table` int32 [requests, blocks] lists
-    its blocks (on the device)."""
+    takes the rows `first[i] * RAISED_ROWS_BLOCK` onward of a matrix of `rows` rows; `table` int32 [requests, blocks] lists,
+    by the block of a POSITION, the block of rows that holds it (on the device).  With a `window` (and the positions
+    `offsets[i]` cached before the step) a request's rows start at the block of the first position that its first new
+    token still sees; earlier positions' entries repeat that block and are never read."""
 
-    def __init__(self, kv_lens, device):
+    def __init__(self, kv_lens, device, offsets=None, window: int = 0):
+        self.window = int(window)
         blocks = [-(-int(n) // RAISED_ROWS_BLOCK) for n in kv_lens]
+        skipped = [0] * len(blocks)
+        if self.window > 0:
+            skipped = [max(0, int(o) + 1 - self.window) // RAISED_ROWS_BLOCK for o in offsets]
         self.max_blocks, self.first, at = max(blocks), [], 0
-        for b in blocks:
+        for b, s in zip(blocks, skipped):
             self.first.append(at)
-            at += b
-        self.rows, self.requests, self.max_kv = at * RAISED_ROWS_BLOCK, len(blocks), int(max(kv_lens))
-        table = [[f + min(j, b - 1) for j in range(self.max_blocks)] for f, b in zip(self.first, blocks)]
+            at += b - s
+        self.rows, self.requests = at * RAISED_ROWS_BLOCK, len(blocks)
+        self.max_kv = int(max(int(n) - s * RAISED_ROWS_BLOCK for n, s in zip(kv_lens, skipped)))   # most rows of a request
+        table = [[f + min(max(j - s, 0), b - s - 1) for j in range(self.max_blocks)] for f, b, s in zip(self.first, blocks, skipped)]
         self.table = torch.tensor(table, dtype=torch.int32).to(device, non_blocking=True)
 
 
 def latent_gather(pool: torch.Tensor, block_table: torch.Tensor, cu_seqlens, kv_offsets, plan: RaisedPlan) -> torch.Tensor:
-    """The cached rows of every request of a step (positions 0 .. kv_offsets + new tokens - 1, new ones included) copied out
-    of their pages into one matrix [plan.rows, row width] where `plan` says; the rows up to the next block are zeros."""
+    """The cached rows of every request of a step (positions 0, or the first block that the plan's window still needs, up to
+    kv_offsets + new tokens - 1, new ones included) copied out of their pages into one matrix [plan.rows, row width] where
+    `plan` says; the rows up to the next block are zeros."""
     _dev(pool, block_table, cu_seqlens, kv_offsets)
     _need(pool.is_contiguous() and pool.dim() == 4 and pool.shape[1] == 1, "latent_gather: a pool [pages, 1, page size, width]")
     _need(block_table.dtype == torch.int32 and block_table.is_contiguous() and block_table.shape[0] >= plan.requests,
           "latent_gather: int32 block table [requests, blocks]")
     rows = torch.empty((plan.rows, pool.shape[3]), dtype=pool.dtype, device=pool.device)
-    _check(library().vx_latent_gather(_ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets), None,
-                                      _ptr(plan.table), plan.max_blocks, _ptr(rows), plan.requests, plan.max_kv, pool.shape[3],
-                                      pool.shape[2], RAISED_ROWS_BLOCK, dtype_code(pool.dtype), _stream()), "latent_gather")
+    _check(library().vx_latent_gather_window(_ptr(pool), _ptr(block_table), block_table.shape[1], _ptr(cu_seqlens), _ptr(kv_offsets),
+                                             None, _ptr(plan.table), plan.max_blocks, _ptr(rows), plan.requests, plan.max_kv,
+                                             pool.shape[3], pool.shape[2], RAISED_ROWS_BLOCK, plan.window, dtype_code(pool.dtype),
+                                             _stream()), "latent_gather")
     return rows
 
 
@@ -1079,18 +1122,108 @@ def raised_attention_supported(dtype, key_dim: int, v_head_dim: int) -> bool:
 
 def raised_attention(q: torch.Tensor, q_row_stride: int, kv: torch.Tensor, cu_seqlens, kv_offsets, plan: RaisedPlan, scale: float,
                      num_heads: int, key_dim: int, v_head_dim: int, max_new: int, softcap: float = 0.0) -> torch.Tensor:
-    """Causal attention of prompt portions over keys and values that a matrix product left as rows `kv`
-    [plan.rows, num_heads * (key_dim + v_head_dim)], a head's key followed by its value, request i's rows where `plan` says.
+    """Causal attention (under the plan's window, if it has one) of prompt portions over keys and values that a matrix product
+    left as rows `kv` [plan.rows, num_heads * (key_dim + v_head_dim)], a head's key followed by its value, request i's rows where `plan` says.
     The tensor-core kernel of `biased_prefill_attention` with other strides.  Returns [tokens, num_heads * v_head_dim]."""
     _dev(q, kv, cu_seqlens, kv_offsets)
     per = key_dim + v_head_dim
     _need(q.dtype == torch.bfloat16 and kv.dtype == torch.bfloat16 and kv.is_contiguous() and kv.shape[1] == num_heads * per,
           "raised_attention: bfloat16 rows of heads * (key + value) elements")
     out = torch.empty((q.shape[0], num_heads * v_head_dim), dtype=q.dtype, device=q.device)
-    _check(library().vx_biased_attention_rows(
+    _check(library().vx_biased_attention_rows_window(
         _ptr(q), int(q_row_stride), _ptr(kv), kv.shape[1], per, kv.data_ptr() + 2 * key_dim, kv.shape[1], per, _ptr(plan.table),
         plan.max_blocks, _ptr(cu_seqlens), _ptr(kv_offsets), None, _ptr(out), out.shape[1], float(scale), plan.requests,
-        int(max_new), num_heads, num_heads, key_dim, v_head_dim, RAISED_ROWS_BLOCK, float(softcap), _stream()), "raised_attention")
+        int(max_new), num_heads, num_heads, key_dim, v_head_dim, RAISED_ROWS_BLOCK, float(softcap), plan.window, _stream()),
+        "raised_attention")
+    return out
+
+
+STREAMS_MAX = 16   # copies of the stream that the stream kernels take
+
+
+def _host_floats(values, n: int, what: str):
+    if values is None:
+        return None
+    vals = [float(v) for v in values]
+    _need(len(vals) == n, "%s: expected %d numbers, got %d" % (what, n, len(vals)))
+    return (c_float * n)(*vals)
+
+
+def stream_norm(x: Optional[torch.Tensor], streams: int, in_coef, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+                rows: Optional[torch.Tensor] = None, single: Optional[torch.Tensor] = None,
+                copies: Optional[torch.Tensor] = None, rms: bool = False) -> torch.Tensor:
+    """The norm of u = sum_s in_coef[s] x_s over the `streams` copies of the stream x float32 [tokens, streams * E]:
+    layer norm without bias (`rms`: RMS norm) times `weight`, in `out_dtype`.  `in_coef`: host numbers (None: ones).
+    With `rows` (int32 on the device) only those tokens.  With `single` float32 [tokens, E] the copies are all equal to
+    it, and are written to `copies` [tokens, streams * E] if given."""
+    src = single if single is not None else x
+    _dev(x, weight, rows, single, copies)
+    tokens = src.shape[0]
+    E = weight.numel()
+    _need(0 < streams <= STREAMS_MAX, "stream_norm: 1 to %d copies of the stream" % STREAMS_MAX)
+    _need(weight.dtype == torch.float32 and src.dtype == torch.float32 and src.is_contiguous()
+          and src.shape[1] == (E if single is not None else streams * E), "stream_norm: float32 rows of streams * width elements")
+    _need(copies is None or (copies.dtype == torch.float32 and copies.is_contiguous() and tuple(copies.shape) == (tokens, streams * E)),
+          "stream_norm: copies [tokens, streams * width] float32")
+    _need(rows is None or rows.dtype == torch.int32, "stream_norm: int32 rows")
+    n_rows = rows.numel() if rows is not None else tokens
+    out = torch.empty((n_rows, E), dtype=out_dtype, device=src.device)
+    _check(library().vx_stream_norm(_ptr(x) if single is None else None, int(streams), _host_floats(in_coef, streams, "stream_norm"),
+                                    _ptr(single), _ptr(copies), _ptr(weight), float(eps), _ptr(rows), n_rows, _ptr(out), tokens, E,
+                                    1 if rms else 0, dtype_code(out_dtype), _stream()), "stream_norm")
+    return out
+
+
+def stream_update(x: torch.Tensor, streams: int, mix, out_coef, mult: float, layer_scale: Optional[torch.Tensor], y: torch.Tensor,
+                  in_next=None, weight_next: Optional[torch.Tensor] = None, eps: float = 0.0, rms: bool = False):
+    """x float32 [tokens, streams * E] in place: x_t <- sum_s mix[s][t] x_s + mult * out_coef[t] * layer_scale (.) y, all
+    copies from the old ones (`mix` rows are "from", host numbers, None: the identity; `out_coef` None: ones; `layer_scale`
+    float32 [E] or None).  With `weight_next` also returns the norm of sum_t in_next[t] x_t of the new copies, in y's type."""
+    _dev(x, layer_scale, y, weight_next)
+    tokens, E = y.shape
+    _need(0 < streams <= STREAMS_MAX and x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (tokens, streams * E),
+          "stream_update: the stream float32 [tokens, streams * width]")
+    _need(y.stride(1) == 1 and (layer_scale is None or (layer_scale.dtype == torch.float32 and layer_scale.numel() == E)),
+          "stream_update: rows contiguous, float32 layer scale [width]")
+    flat = None if mix is None else [v for row in mix for v in row]
+    h = None
+    if weight_next is not None:
+        _need(weight_next.dtype == torch.float32 and weight_next.numel() == E, "stream_update: float32 norm weight [width]")
+        h = torch.empty((tokens, E), dtype=y.dtype, device=y.device)
+    _check(library().vx_stream_update(_ptr(x), int(streams), _host_floats(flat, streams * streams, "stream_update"),
+                                      _host_floats(out_coef, streams, "stream_update"), float(mult), _ptr(layer_scale), _ptr(y),
+                                      y.stride(0), _host_floats(in_next, streams, "stream_update"), _ptr(weight_next), float(eps),
+                                      _ptr(h), tokens, E, 1 if rms else 0, dtype_code(y.dtype), _stream()), "stream_update")
+    return h
+
+
+def diff_combine(maps: torch.Tensor, gates: Optional[torch.Tensor], gate_col: int, lam: float, post: float, eps: float,
+                 num_heads: int, per_group: int, v_head_dim: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """maps [tokens, 2 * num_heads * v_head_dim] (float32 or `out_dtype`), per key/value group the group's `per_group` heads
+    of the first softmax map followed by those of the second: o = a1 - lam a2, divided by its root mean square over the head
+    (eps inside the root), times `post`, times sigmoid of column gate_col + head of the token's row of `gates` (gate_col < 0:
+    no gate).  Returns [tokens, num_heads * v_head_dim] in `out_dtype`, heads in their own order."""
+    _dev(maps, gates)
+    tokens = maps.shape[0]
+    _need(maps.is_contiguous() and maps.shape[1] == 2 * num_heads * v_head_dim and maps.dtype in (torch.float32, out_dtype),
+          "diff_combine: maps [tokens, 2 heads * v_head_dim]")
+    _need(gate_col < 0 or (gates is not None and gates.dtype == out_dtype and gates.stride(1) == 1), "diff_combine: gates of the output's type")
+    out = torch.empty((tokens, num_heads * v_head_dim), dtype=out_dtype, device=maps.device)
+    _check(library().vx_diff_combine(_ptr(maps), 1 if maps.dtype == torch.float32 else 0, _ptr(gates),
+                                     gates.stride(0) if gates is not None else 0, int(gate_col), _ptr(out), float(lam), float(post),
+                                     float(eps), tokens, num_heads, per_group, v_head_dim, dtype_code(out_dtype), _stream()),
+           "diff_combine")
+    return out
+
+
+def sigmoid_gate(o: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
+    """o * sigmoid(gate), element by element; rows may be strided."""
+    _dev(o, gate)
+    _need(o.dim() == 2 and o.shape == gate.shape and o.dtype == gate.dtype and o.stride(1) == 1 and gate.stride(1) == 1,
+          "sigmoid_gate: two matrices of one shape and type, rows contiguous")
+    out = torch.empty(tuple(o.shape), dtype=o.dtype, device=o.device)
+    _check(library().vx_sigmoid_gate(_ptr(o), o.stride(0), _ptr(gate), gate.stride(0), _ptr(out), out.stride(0), o.shape[0],
+                                     o.shape[1], dtype_code(o.dtype), _stream()), "sigmoid_gate")
     return out
 
 

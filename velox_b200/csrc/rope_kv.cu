@@ -28,14 +28,15 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
                                        const float* __restrict__ inv_freq, int rot_dim,
                                        const int* __restrict__ positions,
                                        const int* __restrict__ slot_mapping, T* __restrict__ k_pool,
-                                       T* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv, int interleaved) {
+                                       T* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv, int interleaved,
+                                       int Hv, float magnitude) {
     pdl_wait();
     pdl_trigger();
     extern __shared__ float smem[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int head = blockIdx.y * ROPE_WARPS + warp;
-    if (head >= H + 2 * Hk) return;
+    if (head >= H + Hk + Hv) return;
     float* buf = smem + warp * D;
     T* src = qkv + (size_t)t * row_stride + (size_t)head * D;
     const int slot = slot_mapping ? slot_mapping[t] : -1;
@@ -44,7 +45,7 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
         if (slot < 0) return;
         const int hk = head - H - Hk;
         const T* vsrc = qkv + (size_t)t * row_stride + (size_t)(H + Hk) * D + (size_t)hk * Dv;
-        T* dst = v_pool + (((size_t)(slot / S) * Hk + hk) * S + (slot % S)) * Dv;
+        T* dst = v_pool + (((size_t)(slot / S) * Hv + hk) * S + (slot % S)) * Dv;
         for (int d = lane; d < Dv; d += 32) dst[d] = vsrc[d];
         return;
     }
@@ -70,6 +71,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
         for (int i = lane; i < half; i += 32) {
             float sn, cs;
             sincosf(pos * inv_freq[i], &sn, &cs);
+            sn *= magnitude;
+            cs *= magnitude;
             const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
             const float a = buf[ia], b = buf[ib];
             buf[ia] = a * cs - b * sn;
@@ -220,19 +223,23 @@ qk_norm_rope_kv_128_row_kernel(bf16* __restrict__ qkv, int row_stride, const flo
     }
 }
 
-extern "C" int vx_qk_norm_rope_kv_pairs(void* qkv, int row_stride, const float* q_weight,
-                                        const float* k_weight, float eps, const float* inv_freq,
-                                        int rot_dim, const int* positions, const int* slot_mapping,
-                                        void* k_pool, void* v_pool, int tokens, int H, int Hk, int D, int S,
-                                        int dtype, int Dv, int interleaved, cudaStream_t stream) {
+// `Hv` value heads follow the key heads in a row (0: as many as key heads; fewer where several key heads share a
+// value head: the value pool is then [page, Hv, S, Dv]); cosines and sines are multiplied by `magnitude` (a rotation
+// whose frequencies were stretched may lengthen the rotated channels by a fixed factor).
+extern "C" int vx_qk_norm_rope_kv_shared(void* qkv, int row_stride, const float* q_weight,
+                                         const float* k_weight, float eps, const float* inv_freq,
+                                         int rot_dim, const int* positions, const int* slot_mapping,
+                                         void* k_pool, void* v_pool, int tokens, int H, int Hk, int D, int S,
+                                         int dtype, int Dv, int interleaved, int Hv, float magnitude, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
     if (Dv <= 0) Dv = D;
+    if (Hv <= 0) Hv = Hk;
     if (H <= 0 || Hk <= 0 || D <= 0 || S <= 0 || D > ROPE_MAX_D || Dv > ROPE_MAX_D) return VX_ERR_SHAPE;
     if (rot_dim < 0 || rot_dim > D || (rot_dim & 1)) return VX_ERR_SHAPE;
-    if (row_stride < (H + Hk) * D + Hk * Dv) return VX_ERR_SHAPE;
+    if (row_stride < (H + Hk) * D + Hv * Dv) return VX_ERR_SHAPE;
     if (slot_mapping && (!k_pool || !v_pool)) return VX_ERR_SHAPE;
     if (!inv_freq || rot_dim == 0) interleaved = 0;
-    if (!interleaved && dtype == VX_BF16 && D == 128 && Dv == D && (rot_dim == D || !inv_freq) && !(row_stride & 3) &&
+    if (Hv == Hk && magnitude == 1.f && !interleaved && dtype == VX_BF16 && D == 128 && Dv == D && (rot_dim == D || !inv_freq) && !(row_stride & 3) &&
         !((((uintptr_t)qkv) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool)) & 7)) {
         if (tokens >= ROPE128_TOKEN_MIN) {
             VX_LAUNCH_K(VX_K_ROPE, qk_norm_rope_kv_128_row_kernel, tokens, ROPE128_WARPS * 32, 0, stream, (bf16*)qkv,
@@ -248,18 +255,27 @@ extern "C" int vx_qk_norm_rope_kv_pairs(void* qkv, int row_stride, const float* 
         VX_LAUNCH_CHECK();
         return VX_OK;
     }
-    dim3 grid(tokens, (H + 2 * Hk + ROPE_WARPS - 1) / ROPE_WARPS);
+    dim3 grid(tokens, (H + Hk + Hv + ROPE_WARPS - 1) / ROPE_WARPS);
     const size_t smem = (size_t)ROPE_WARPS * D * sizeof(float);
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<float>), grid, ROPE_WARPS * 32, smem, stream, (float*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
-            (float*)k_pool, (float*)v_pool, H, Hk, D, S, Dv, interleaved);
+            (float*)k_pool, (float*)v_pool, H, Hk, D, S, Dv, interleaved, Hv, magnitude);
     else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_kernel<bf16>), grid, ROPE_WARPS * 32, smem, stream, (bf16*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
-            (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S, Dv, interleaved);
+            (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S, Dv, interleaved, Hv, magnitude);
     else
         return VX_ERR_DTYPE;
     VX_LAUNCH_CHECK();
     return VX_OK;
+}
+
+extern "C" int vx_qk_norm_rope_kv_pairs(void* qkv, int row_stride, const float* q_weight,
+                                        const float* k_weight, float eps, const float* inv_freq,
+                                        int rot_dim, const int* positions, const int* slot_mapping,
+                                        void* k_pool, void* v_pool, int tokens, int H, int Hk, int D, int S,
+                                        int dtype, int Dv, int interleaved, cudaStream_t stream) {
+    return vx_qk_norm_rope_kv_shared(qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
+                                     k_pool, v_pool, tokens, H, Hk, D, S, dtype, Dv, interleaved, 0, 1.f, stream);
 }
 
 // The half-split rotation under its first name.

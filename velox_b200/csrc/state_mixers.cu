@@ -416,12 +416,13 @@ __global__ void latent_prep_kernel(const T* __restrict__ down, int ldd, T* q, in
     const float pos = (float)positions[t];
     const int half = R >> 1;
     const int slot = slot_mapping ? slot_mapping[t] : -1;
-    const T* dr = down + (size_t)t * ldd;
+    const T* dr = down ? down + (size_t)t * ldd : nullptr;   // (no row of its own: a layer that reads another's cache)
     float ss = 0.f;
-    for (int i = threadIdx.x; i < C; i += blockDim.x) { const float v = to_f32(dr[i]); ss += v * v; }
+    if (dr && slot >= 0)
+        for (int i = threadIdx.x; i < C; i += blockDim.x) { const float v = to_f32(dr[i]); ss += v * v; }
     ss = block_sum(ss, scratch);
     const float rstd = rsqrtf(ss / (float)C + eps);
-    if (slot >= 0) {
+    if (dr && slot >= 0) {
         T* dst = pool + (size_t)slot * (C + R);
         for (int i = threadIdx.x; i < C; i += blockDim.x) dst[i] = from_f32<T>(to_f32(dr[i]) * rstd * w[i]);
         for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -450,9 +451,9 @@ extern "C" int vx_latent_prep(const void* down, int ldd, void* q, int ldq, void*
                               const float* inv_freq, int interleaved, const int* positions, const int* slot_mapping,
                               void* pool, int tokens, int H, int D, int R, int C, int dtype, cudaStream_t stream) {
     if (tokens <= 0) return VX_OK;
-    if (H <= 0 || D < 0 || R < 0 || (R & 1) || C <= 0 || ldd < C + R || ldq < H * (D + R)) return VX_ERR_SHAPE;
+    if (H <= 0 || D < 0 || R < 0 || (R & 1) || C <= 0 || (down && ldd < C + R) || ldq < H * (D + R)) return VX_ERR_SHAPE;
     if (R > 0 && !inv_freq) return VX_ERR_SHAPE;
-    if (slot_mapping && !pool) return VX_ERR_SHAPE;
+    if (slot_mapping && (!pool || !down)) return VX_ERR_SHAPE;
     const int threads = C >= 512 ? 256 : 128;
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ROPE, (latent_prep_kernel<float>), tokens, threads, 0, stream, (const float*)down, ldd, (float*)q, ldq, (float*)qa, w, eps, inv_freq, interleaved, positions, slot_mapping, (float*)pool, H, D, R, C);

@@ -1,4 +1,4 @@
-from . import buvuzen, dobepel, kapuvik, qwen3  # register the architectures
+from . import buvuzen, dobepel, fovenex, kapuvik, qwen3  # register the architectures
 from .decoder import DecoderModel
 
-__all__ = ["DecoderModel", "buvuzen", "dobepel", "kapuvik", "qwen3"]
+__all__ = ["DecoderModel", "buvuzen", "dobepel", "fovenex", "kapuvik", "qwen3"]

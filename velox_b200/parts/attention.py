@@ -201,7 +201,8 @@ class PagedAttention(Mixer):
             inv_freq, rot = rotary if rotary is not None else (None, 0)
             ops.qk_norm_rope_kv(qkv, qw, kw, self.eps, inv_freq, rot, ctx.positions, slots,
                                 cache.k_pool, cache.v_pool, H, Hk, D, self.v_head_dim,
-                                interleaved=bool(getattr(self.position, "interleaved", False)))
+                                interleaved=bool(getattr(self.position, "interleaved", False)),
+                                magnitude=float(getattr(self.position, "magnitude", 1.0)))
         else:
             # An encoding the fused kernel does not know: norm in place, let the
             # part encode q and k in place, then write the cache.

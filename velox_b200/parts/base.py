@@ -38,6 +38,7 @@ class TensorSpec:
       norm:          1 + N(0, 0.05); held in float32 (an exact widening)
       bias:          N(0, 0.02); held in float32
       matrix_f32:    N(0, 0.02); held in float32 whatever the engine's element type (a router)
+      mixing:        identity + N(0, 0.05), square; held in float32 (how the copies of a stream are mixed)
       int_table:     integers; held as int32
     A dimension of -1 is left open: the file's tensor decides it, and the part reads it off when it binds."""
     name: str
@@ -56,24 +57,32 @@ class PagedKV:
     """Keys and values of every position in pages; with a window only the last
     `window` positions are ever read, and older pages are given back, except those
     that hold one of the first `keep_first` positions (which every query still
-    reads).  `v_head_dim` is the size of a value where it is not a key's (0: the same)."""
+    reads).  `v_head_dim` is the size of a value where it is not a key's (0: the same);
+    `num_v_heads` the number of value heads where several key heads share one (0: one per key head)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
     v_head_dim: int = 0
     keep_first: int = 0
+    num_v_heads: int = 0
 
     @property
     def value_dim(self) -> int:
         return self.v_head_dim or self.head_dim
+
+    @property
+    def value_heads(self) -> int:
+        return self.num_v_heads or self.num_kv_heads
 
 
 @dataclass(frozen=True)
 class PagedLatent:
     """One row of `width` elements per position in pages: what a latent attention keeps (the normed latent vector
     followed by the rotated key part that its heads share).  Keys and values are raised from it, so nothing is
-    stored per head."""
+    stored per head.  With a `window` only the last `window` positions are ever read (by the layer that fills the rows
+    and by every layer that borrows them), and older pages are given back."""
     width: int
+    window: int = 0
 
 
 @dataclass(frozen=True)

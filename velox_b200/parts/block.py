@@ -29,6 +29,16 @@ travel as a `PendingSum` to whoever norms the stream next (the next block of thi
 block or the final norm), whose one kernel adds them to the float32 residual, with their coefficients, and norms the
 sum.  A mixer made of members side by side hands its members over unmerged with their coefficients
 (`forward_terms`), so their weighted sum is formed in float32 in that same kernel.
+
+`HyperConnectionBlock`: the stream is kept in n copies x_1 .. x_n (all equal to the embedding's output at first).  A
+sublayer reads a weighted sum of them and writes to all of them while they are mixed among themselves:
+    u = sum_s in[s] x_s;   y = ls (.) sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + m out[t] y   (all t from the old x_s)
+with `in`, `out` [n], `mix` [n, n] (indexed [from, to]) and the channel-wise layer scale `ls` [hidden] being tensors of the
+sublayer, and m a constant of the model.  With `streams` = 0 there is one copy and no mixing tensors: the plain pre-norm
+layer with a layer scale, x <- x + m ls (.) sublayer(norm(x)).  The update of one sublayer and the weighted sum and norm
+of the next are one kernel (`ops.stream_update`); the last update of a block travels as a `PendingStreams` to the next
+block of this kind, whose first norm it is fused with, or is applied by whoever reads the stream next.  The residual
+between such blocks is [tokens, n * hidden] float32; a `LayerNorm(streams=n)` reads the sum of the copies at the end.
 """
 from __future__ import annotations
 
@@ -38,7 +48,7 @@ from typing import List, Optional, Tuple
 import torch
 
 from ..csrc import ops
-from .base import Block
+from .base import Block, Part, TensorSpec
 
 
 @dataclass
@@ -155,3 +165,110 @@ class ParallelSublayersBlock(Block):
         if self.feed_forward is not None:
             terms.append((self.feed_forward.forward(h, ctx), 1.0))
         return residual, PendingSum(terms)
+
+
+class PendingStreams(PendingSum):
+    """A sublayer's output that is still to be written into the copies of the stream: x_t <- sum_s mix[s][t] x_s +
+    mult * out[t] * layer_scale (.) y.  `add_to` applies it (and, given the next reader's coefficients and norm weight,
+    returns that reader's normed input from the same kernel)."""
+
+    def __init__(self, y, streams: int, mix, out, mult: float, layer_scale):
+        super().__init__([(y, 1.0)])
+        self.y, self.streams, self.mix, self.out, self.mult, self.layer_scale = y, int(streams), mix, out, float(mult), layer_scale
+
+    def add_to(self, residual, weight=None, eps: float = 0.0, out_dtype=None, in_next=None, rms: bool = False):
+        if self.rows is not None or self.vector is not None or len(self.terms) != 1:
+            raise ValueError("a stream kept in several copies takes no inputs between its layers")
+        return ops.stream_update(residual, self.streams, self.mix, self.out, self.mult, self.layer_scale, self.y,
+                                 in_next, weight, eps, rms)
+
+
+class StreamCoefficients(Part):
+    """The tensors of one sublayer's connection to the copies of the stream: `in`, `out` [n], `mix` [n, n] (kept as host
+    numbers: they are parameters of the stream kernels) and the layer scale [hidden] (float32 on the device)."""
+    cuda_graph_safe = True
+
+    def __init__(self, prefix: str, streams: int, hidden_size: int, names=("in", "out", "mix"), scale_name: str = ""):
+        super().__init__(prefix)
+        self.streams, self.hidden_size = int(streams), int(hidden_size)
+        self.names = tuple(prefix + n for n in names)
+        self.scale_name = scale_name
+        self.into = self.out = self.mix = self.layer_scale = None
+
+    def tensor_specs(self):
+        n, specs = self.streams, []
+        if n:
+            specs += [TensorSpec(self.names[0], (n,), "norm"), TensorSpec(self.names[1], (n,), "norm"),
+                      TensorSpec(self.names[2], (n, n), "mixing")]
+        if self.scale_name:
+            specs.append(TensorSpec(self.scale_name, (self.hidden_size,), "norm"))
+        return specs
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        if self.streams:
+            self.into = tensors[self.names[0]].to(torch.float32).cpu().tolist()
+            self.out = tensors[self.names[1]].to(torch.float32).cpu().tolist()
+            self.mix = tensors[self.names[2]].to(torch.float32).cpu().tolist()
+        if self.scale_name:
+            self.layer_scale = tensors[self.scale_name].to(torch.float32).contiguous()
+
+
+class HyperConnectionBlock(Block):
+    needs_feed_forward = False
+    takes_pending = True
+
+    def __init__(self, mixer, feed_forward, norms, hidden_size: int, streams: int = 0, residual_mult: float = 1.0,
+                 prefix: str = "", connection_names=("hc1.", "hc2."), scale_names=("ls1", "ls2"), coefficient_names=("in", "out", "mix")):
+        self.norm_names = ("mixer",) + (("feed_forward",) if feed_forward is not None else ())
+        super().__init__(mixer, feed_forward, norms)
+        self.hidden_size, self.streams, self.residual_mult = int(hidden_size), int(streams), float(residual_mult)
+        if not 0 <= self.streams <= ops.STREAMS_MAX:
+            raise ValueError("%sa stream in %d copies: the stream kernels take up to %d" % (prefix, self.streams, ops.STREAMS_MAX))
+        for name, n in self.norms.items():
+            if not hasattr(n, "weight") or not hasattr(n, "eps") or getattr(n, "streams", 1) != 1:
+                raise ValueError("HyperConnectionBlock fuses its norms into the stream's update and takes layer or RMS norms of one "
+                                 "row; %r is %s" % (name, type(n).__name__))
+        self.links = [StreamCoefficients(prefix + connection_names[q], self.streams, self.hidden_size, coefficient_names,
+                                         prefix + scale_names[q] if scale_names and scale_names[q] else "")
+                      for q in range(2 if feed_forward is not None else 1)]
+
+    @property
+    def copies(self) -> int:
+        return max(self.streams, 1)
+
+    def parts(self):
+        return super().parts() + list(self.links)
+
+    @staticmethod
+    def _rms(norm) -> bool:
+        return not hasattr(norm, "streams")   # (an RMS norm of this package; the layer norm says how many copies it reads)
+
+    def forward(self, residual, delta, ctx, cache):
+        n, E = self.copies, self.hidden_size
+        norm, link = self.norms["mixer"], self.links[0]
+        dtype = self.mixer.runtime.dtype
+        if residual.shape[1] == E and n > 1 or (residual.shape[1] == E and not isinstance(delta, PendingStreams)):
+            # the embedding's output (or a plain stream left by another kind of block): the copies start equal to it
+            if isinstance(delta, PendingSum):
+                delta.add_to(residual)
+            elif delta is not None:
+                ops.sum_add_rmsnorm(residual, [(delta, 1.0)])
+            copies = torch.empty((residual.shape[0], n * E), dtype=torch.float32, device=residual.device) if n > 1 else None
+            h = ops.stream_norm(None, n, link.into, norm.weight, norm.eps, dtype, single=residual, copies=copies, rms=self._rms(norm))
+            if copies is not None:
+                residual = copies
+        elif isinstance(delta, PendingStreams):
+            h = delta.add_to(residual, norm.weight, norm.eps, dtype, in_next=link.into, rms=self._rms(norm))
+        else:
+            if delta is not None:
+                raise ValueError("a stream kept in several copies cannot take a sublayer output that names no copies")
+            h = ops.stream_norm(residual, n, link.into, norm.weight, norm.eps, dtype, rms=self._rms(norm))
+        y = self.mixer.forward(h, ctx, cache)
+        pending = PendingStreams(y, n, link.mix, link.out, self.residual_mult, link.layer_scale)
+        if self.feed_forward is not None:
+            norm, link = self.norms["feed_forward"], self.links[1]
+            h = pending.add_to(residual, norm.weight, norm.eps, dtype, in_next=link.into, rms=self._rms(norm))
+            y = self.feed_forward.forward(h, ctx)
+            pending = PendingStreams(y, n, link.mix, link.out, self.residual_mult, link.layer_scale)
+        return residual, pending

@@ -16,6 +16,17 @@ kernel takes) goes the other way round: the cached rows of its requests are copi
 product with [W_uk,h 0; 0 I; W_uv,h 0] per head leaves every head's key [W_uk,h c ; r] and value side by side, and the
 tensor-core prompt kernel (`ops.raised_attention`) reads them there with the queries as the projection left them.
 Angles, the latent norm, scores and the softmax are float32.  The rotation takes either layout of the position part.
+
+Four more, for designs that have them:
+`q_rank` r > 0: the queries go through a latent vector of their own, q = W_uq rmsnorm(W_dq h) (a plain weight, the
+layer's eps); W_dq rides in the fused projection and W_uq is a second product;
+`window` w > 0: position i sees only j with 0 <= i - j < w.  The folded kernel starts at the window's first tile; the
+raised way gathers and raises only the rows from the window of the step's first query on (`cache_window`, at least
+`window`, is how long the cache keeps a row: the longest window of this layer and of the layers that borrow its rows);
+`output_gate`: the joined heads are multiplied element by element by sigmoid(W_g h) before the output projection; W_g rides
+in the fused projection;
+`own_rows=False`: the layer has no W_dkv and no norm weight of its own and reads the rows that another layer wrote (the
+plan's `cache_of`), with its own W_uk, W_uv, queries and window.
 """
 from __future__ import annotations
 
@@ -41,8 +52,19 @@ class LatentAttention(Mixer):
 
     def __init__(self, prefix: str, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int, v_head_dim: int,
                  kv_rank: int, scale: float, position: PartSpec, eps: float = 1e-6,
-                 names: Sequence[str] = ("q", "dkv", "dkv.norm", "uk", "uv", "o")):
+                 names: Sequence[str] = ("q", "dkv", "dkv.norm", "uk", "uv", "o"), q_rank: int = 0, window: int = 0,
+                 cache_window: Optional[int] = None, output_gate: bool = False, own_rows: bool = True,
+                 query_names: Sequence[str] = ("dq", "dq.norm", "uq"), gate_name: str = "g"):
         super().__init__(prefix)
+        self.q_rank, self.window, self.output_gate, self.own_rows = int(q_rank), int(window), bool(output_gate), bool(own_rows)
+        self.cache_window = self.window if cache_window is None else int(cache_window)
+        if self.q_rank < 0 or self.window < 0 or (self.cache_window and self.cache_window < self.window) \
+                or (self.window == 0 and self.cache_window):
+            raise ValueError("%slatent attention: q_rank and window must not be negative, and the cache must keep a row at "
+                             "least as long as the window" % prefix)
+        self.query_names = tuple(prefix + n for n in query_names)
+        self.gate_name = prefix + gate_name
+        self.q_norm_weight = self.uq = None
         self.hidden_size, self.num_heads, self.head_dim = int(hidden_size), int(num_heads), int(head_dim)
         self.rot_dim, self.v_head_dim, self.kv_rank = int(rot_dim), int(v_head_dim), int(kv_rank)
         self.scale, self.eps = float(scale), float(eps)
@@ -55,6 +77,9 @@ class LatentAttention(Mixer):
         table = self.position.rotary_table("cpu")
         if table is None or table[1] != self.rot_dim:
             raise ValueError("%sthe rotated part has %d channels and the position encoding must turn all of them" % (prefix, self.rot_dim))
+        if getattr(self.position, "magnitude", 1.0) != 1.0:
+            raise ValueError("%slatent attention rotates without a multiplier of cosines and sines; the position asks for %g"
+                             % (prefix, self.position.magnitude))
         self.names = dict(zip(("q", "dkv", "norm", "uk", "uv", "o"), (prefix + n for n in names)))
         self.proj: Optional[Linear] = None
         self.out: Optional[Linear] = None
@@ -66,17 +91,42 @@ class LatentAttention(Mixer):
 
     def tensor_specs(self) -> List[TensorSpec]:
         e, H, n = self.hidden_size, self.num_heads, self.names
-        return [TensorSpec(n["q"], (H * (self.head_dim + self.rot_dim), e), "matrix"),
-                TensorSpec(n["dkv"], (self.row, e), "matrix"), TensorSpec(n["norm"], (self.kv_rank,), "norm"),
-                TensorSpec(n["uk"], (H * self.head_dim, self.kv_rank), "matrix"),
-                TensorSpec(n["uv"], (H * self.v_head_dim, self.kv_rank), "matrix"),
-                TensorSpec(n["o"], (e, H * self.v_head_dim), "matrix")] + self.position.tensor_specs()
+        q_rows = H * (self.head_dim + self.rot_dim)
+        if self.q_rank:
+            dq, dq_norm, uq = self.query_names
+            specs = [TensorSpec(dq, (self.q_rank, e), "matrix"), TensorSpec(dq_norm, (self.q_rank,), "norm"),
+                     TensorSpec(uq, (q_rows, self.q_rank), "matrix")]
+        else:
+            specs = [TensorSpec(n["q"], (q_rows, e), "matrix")]
+        if self.own_rows:
+            specs += [TensorSpec(n["dkv"], (self.row, e), "matrix"), TensorSpec(n["norm"], (self.kv_rank,), "norm")]
+        if self.output_gate:
+            specs.append(TensorSpec(self.gate_name, (H * self.v_head_dim, e), "matrix"))
+        return specs + [TensorSpec(n["uk"], (H * self.head_dim, self.kv_rank), "matrix"),
+                        TensorSpec(n["uv"], (H * self.v_head_dim, self.kv_rank), "matrix"),
+                        TensorSpec(n["o"], (e, H * self.v_head_dim), "matrix")] + self.position.tensor_specs()
 
     def bind(self, tensors: Dict[str, torch.Tensor], runtime: Runtime) -> None:
         super().bind(tensors, runtime)
         n, H = self.names, self.num_heads
-        self.proj = Linear(torch.cat([tensors[n["q"]], tensors[n["dkv"]]], dim=0).contiguous())
-        self.norm_weight = tensors[n["norm"]]
+        # one projection of the layer's input: [W_q or W_dq; W_dkv; W_g], every block on a multiple of 8 rows so that the
+        # slices of its output start on 16-byte addresses
+        mats, self.cols, at = [], {}, 0
+        first = tensors[self.query_names[0]] if self.q_rank else tensors[n["q"]]
+        for key, w in (("q", first), ("dkv", tensors[n["dkv"]] if self.own_rows else None),
+                       ("g", tensors[self.gate_name] if self.output_gate else None)):
+            if w is None:
+                continue
+            self.cols[key] = at
+            pad = (-w.shape[0]) % 8
+            mats += [w] + ([torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)] if pad else [])
+            at += w.shape[0] + pad
+        self.proj = Linear(torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0])
+        del mats, first
+        if self.q_rank:
+            self.q_norm_weight = tensors[self.query_names[1]]
+            self.uq = Linear(tensors[self.query_names[2]])
+        self.norm_weight = tensors[n["norm"]] if self.own_rows else None
         # W_uk per head, transposed: [H, kv_rank, head_dim], the matrix of the product that folds it into a query
         self.uk_t = tensors[n["uk"]].view(H, self.head_dim, self.kv_rank).transpose(1, 2).contiguous()
         self.uv = tensors[n["uv"]].view(H, self.v_head_dim, self.kv_rank).contiguous()
@@ -93,33 +143,51 @@ class LatentAttention(Mixer):
         self.rotary = self.position.rotary_table(runtime.device)
 
     def cache_spec(self):
-        return PagedLatent(self.row)
+        if not self.own_rows:
+            return None
+        return PagedLatent(self.row, self.cache_window)
+
+    def _gated(self, o: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        if not self.output_gate:
+            return o
+        g = self.cols["g"]
+        return ops.sigmoid_gate(o, x[:, g:g + o.shape[1]])
 
     def forward(self, h: torch.Tensor, ctx, cache) -> torch.Tensor:
         H, D, R, C, Dv = self.num_heads, self.head_dim, self.rot_dim, self.kv_rank, self.v_head_dim
         t = h.shape[0]
         group = ctx.groups[cache.group]
-        x = self.proj(h)                       # [tokens, H (D + R) | C + R]
-        q, down = x[:, :H * (D + R)], x[:, H * (D + R):]
+        x = self.proj(h)                       # [tokens, H (D + R) or q_rank | C + R | H Dv], each block padded to 8 columns
+        if self.q_rank:
+            q = self.uq(ops.rmsnorm(x[:, :self.q_rank], self.q_norm_weight, self.eps))
+        else:
+            q = x[:, :H * (D + R)]
+        writes = cache.writes and self.own_rows
+        down = x[:, self.cols["dkv"]:self.cols["dkv"] + C + R] if self.own_rows else None
+        slots = group.slot_mapping if writes else None
         interleaved = bool(getattr(self.position, "interleaved", False))
         if (self.raise_w is not None and ctx.max_new >= RAISE_MIN_TOKENS and len(ctx.new_lens) == ctx.n_seqs
-                and len(ctx.offsets) == ctx.n_seqs and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
-            plan = getattr(ctx, "raised_rows", None)   # (made by the step's first latent layer, kept on its context)
+                and len(ctx.offsets) == ctx.n_seqs and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0):
+            plans = getattr(ctx, "raised_rows", None)   # (made by the step's first latent layer of a window, kept on its context)
+            if plans is None:
+                plans = ctx.raised_rows = {}
+            plan = plans.get(self.window)
             if plan is None:
-                plan = ctx.raised_rows = ops.RaisedPlan([a + b for a, b in zip(ctx.offsets, ctx.new_lens)], x.device)
+                plan = plans[self.window] = ops.RaisedPlan([a + b for a, b in zip(ctx.offsets, ctx.new_lens)], x.device,
+                                                           ctx.offsets, self.window)
             if plan.rows * H * (D + R + Dv) * 2 <= RAISE_MAX_BYTES:
                 ops.latent_prep(down, q, None, self.norm_weight, self.eps, self.rotary[0], interleaved, ctx.positions,
-                                group.slot_mapping if cache.writes else None, cache.pages, H, D, R, C)
+                                slots, cache.pages, H, D, R, C)
                 kv = self.raise_w(ops.latent_gather(cache.pages, group.block_table, ctx.cu_seqlens, ctx.kv_offsets, plan))
-                o = ops.raised_attention(x, x.shape[1], kv, ctx.cu_seqlens, ctx.kv_offsets, plan, self.scale, H, D + R, Dv,
+                o = ops.raised_attention(q, q.stride(0), kv, ctx.cu_seqlens, ctx.kv_offsets, plan, self.scale, H, D + R, Dv,
                                          ctx.max_new)
-                return self.out(o)
+                return self.out(self._gated(o, x))
         qa = torch.empty((t, H, C + R), dtype=x.dtype, device=x.device)   # folded queries: [W_uk^T q | rotated part]
         ops.latent_prep(down, q, qa, self.norm_weight, self.eps, self.rotary[0], interleaved,
-                        ctx.positions, group.slot_mapping if cache.writes else None, cache.pages, H, D, R, C)
+                        ctx.positions, slots, cache.pages, H, D, R, C)
         ops.gemm_heads(q.view(t, H, D + R)[:, :, :D], self.uk_t, qa[:, :, :C])
         latent = ops.latent_attention(qa, cache.pages, group.block_table, ctx.seq_of_token, ctx.positions, self.scale, H, C, R,
-                                      max_kv=ctx.max_kv)
+                                      max_kv=ctx.max_kv, window=self.window)
         o = torch.empty((t, H, Dv), dtype=x.dtype, device=x.device)
         ops.gemm_heads(latent, self.uv, o)
-        return self.out(o.view(t, H * Dv))
+        return self.out(self._gated(o.view(t, H * Dv), x))

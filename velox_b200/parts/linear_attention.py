@@ -118,6 +118,9 @@ class DecayedLinearAttention(_LinearAttention):
         if self.position is not None:
             if activation != "none":
                 raise ValueError("%sa rotation of q and k goes with no activation on them" % prefix)
+            if getattr(self.position, "magnitude", 1.0) != 1.0:
+                raise ValueError("%sthe state walk rotates without a multiplier of cosines and sines; the position asks for %g"
+                                 % (prefix, self.position.magnitude))
             if self.position.rotary_table("cpu") is None:
                 raise ValueError("%sthe recurrence kernel rotates by a rotary table; %s has none"
                                  % (prefix, type(self.position).__name__))

@@ -11,7 +11,7 @@ Element types on the device:
   matrices and tables: the engine's element type (bfloat16 files stay
     bfloat16 in a bfloat16 engine; the 32-bit engine widens them exactly);
   norm weights, biases and matrices that are applied in 32 bits whatever the engine
-    (a router): float32 (exact for bfloat16 files; a tensor stored in 32 bits stays so);
+    (a router, the mixing of a stream's copies): float32 (exact for bfloat16 files; a tensor stored in 32 bits stays so);
   integer tables: int32.
 """
 from __future__ import annotations
@@ -50,7 +50,7 @@ _INTS = (torch.int32, torch.int64, torch.int16, torch.int8, torch.uint8)
 def held_dtype(role: str, stored: torch.dtype, runtime: Runtime) -> torch.dtype:
     if role == "int_table":
         return torch.int32
-    if role in ("norm", "bias", "matrix_f32"):
+    if role in ("norm", "bias", "matrix_f32", "mixing"):
         return torch.float32
     return runtime.dtype
 

@@ -2,7 +2,7 @@
 configuration and a seed.
 
 Matrices and tables are N(0, 0.02), norm weights 1 + N(0, 0.05), biases
-N(0, 0.02), integer tables uniform.  Every tensor has its own generator keyed by
+N(0, 0.02), integer tables uniform, mixing matrices of a stream's copies the identity + N(0, 0.05).  Every tensor has its own generator keyed by
 (seed, tensor name), so a tensor's values do not depend on which other tensors
 the model has or on the order they are made in.  Values are rounded to the
 stored element type (bfloat16 by default), so that an engine in either
@@ -40,7 +40,9 @@ def random_tensor(spec: TensorSpec, seed: int, dtype: torch.dtype, device="cpu")
     if spec.role == "int_table":
         return torch.randint(0, 1 << 15, spec.shape, generator=g, dtype=torch.int32, device=device)
     x = torch.randn(spec.shape, generator=g, dtype=torch.float32, device=device)
-    if spec.role == "norm":
+    if spec.role == "mixing":
+        x = torch.eye(spec.shape[0], spec.shape[-1], dtype=torch.float32, device=device) + NORM_STD * x
+    elif spec.role == "norm":
         x = 1.0 + NORM_STD * x
     elif spec.role == "bias":
         x = BIAS_STD * x
@@ -82,6 +84,6 @@ def bind_random_weights(model, runtime, seed: int) -> None:
 
     def make(name: str) -> torch.Tensor:
         s = specs[name]
-        t = random_tensor(s, seed, torch.float32 if s.role in ("norm", "bias", "matrix_f32") else runtime.dtype, runtime.device)
+        t = random_tensor(s, seed, torch.float32 if s.role in ("norm", "bias", "matrix_f32", "mixing") else runtime.dtype, runtime.device)
         return t.to(held_dtype(s.role, t.dtype, runtime)).contiguous()
     model.bind(OnDemand(make, specs), runtime)   # (made when a part binds them: see `load_weights`)
