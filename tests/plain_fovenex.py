@@ -110,7 +110,8 @@ def differential_attention(h, P, m, positions, eps, store=same):
     out = np.zeros((T, H, Dv))
     for hd in range(H):
         g = hd // (H // G)
-        maps = [masked_softmax((q[:, 2 * hd + i] @ k[:, 2 * g + i].T) * m["scale"]) @ v[:, g] for i in (0, 1)]
+        window = int((m.get("mask") or {}).get("size") or 0)
+        maps = [masked_softmax((q[:, 2 * hd + i] @ k[:, 2 * g + i].T) * m["scale"], window) @ v[:, g] for i in (0, 1)]
         o = maps[0] - lam * maps[1]
         out[:, hd] = unit_rms(o, eps) * (1.0 - m["diff"]) * gate[:, hd:hd + 1]
     return store(store(out.reshape(T, H * Dv)) @ P["o"].T)
@@ -132,8 +133,11 @@ def latent_attention(h, P, m, positions, eps, rows, store=same):
     T = h.shape[0]
     H, D, R, Dv = m["heads"], m["dim"], m["rot_dim"], m["vdim"]
     c, r = rows
-    cq = store(unit_rms(store(h @ P["dq"].T), eps) * P["dq.norm"])
-    q = store(cq @ P["uq"].T).reshape(T, H, D + R)
+    if "dq" in P:
+        cq = store(unit_rms(store(h @ P["dq"].T), eps) * P["dq.norm"])
+        q = store(cq @ P["uq"].T).reshape(T, H, D + R)
+    else:   # (queries straight from the layer's input)
+        q = store(h @ P["q"].T).reshape(T, H, D + R)
     q = np.concatenate([q[..., :D], store(rotate_half(q[..., D:], positions, dict(m["rot"], dims=R)))], axis=-1)
     k = store(c @ P["uk"].T).reshape(T, H, D)
     v = store(c @ P["uv"].T).reshape(T, H, Dv)
@@ -192,3 +196,13 @@ def forward(config, tensors, tokens, store=same, layers_out=None):
             layers_out.append(X.sum(axis=0))
     x = store(layer_norm(X.sum(axis=0), np.asarray(tensors["final.norm"], dtype=np.float64), eps))
     return x @ np.asarray(tensors["head"], dtype=np.float64).T
+
+
+def greedy_generate(config, tensors, prompt, n):
+    """The n tokens that follow `prompt` when the most likely one is taken every time (the lowest index among equals)."""
+    toks, out = list(prompt), []
+    for _ in range(n):
+        nxt = int(np.argmax(forward(config, tensors, toks)[-1]))
+        out.append(nxt)
+        toks.append(nxt)
+    return out

@@ -128,6 +128,16 @@ class DifferentialAttention(Mixer):
     def _maps(self, qkv, ctx, cache, group) -> torch.Tensor:
         """Both maps of every head, [tokens, 2 * heads * v_head_dim]: per kv head its heads' first maps, then their second."""
         H, G, D, Dv = self.num_heads, self.num_kv_heads, self.head_dim, self.v_head_dim
+        if ops.biased_attention_supported(qkv.dtype, D, Dv, cache.k_pool.shape[2]):
+            # bfloat16 and sizes the tensor-core kernels take (softmax weights in two bfloat16 halves): a step of single tokens
+            # has every row's keys dealt to the warps of a block, any other step runs the portion kernel
+            if ctx.decode_only:
+                return ops.biased_decode_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table,
+                                                   ctx.seq_of_token, ctx.positions, self.scale, self.window, 0, 0.0, 2 * H, 2 * G, D,
+                                                   Dv, qkv.shape[0], max_kv=ctx.max_kv, v_share=2, out_float32=True)
+            return ops.biased_prefill_attention(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.cu_seqlens,
+                                                ctx.kv_offsets, self.scale, self.window, 0, 0.0, 2 * H, 2 * G, D, Dv, ctx.n_seqs,
+                                                ctx.max_new, qkv.shape[0], v_share=2, out_float32=True)
         return ops.paged_attention_generic(qkv, qkv.shape[1], cache.k_pool, cache.v_pool, group.block_table, ctx.seq_of_token,
                                            ctx.positions, self.scale, self.window, 2 * H, 2 * G, D, qkv.shape[0], v_head_dim=Dv,
                                            v_share=2, out_float32=True)
