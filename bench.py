@@ -734,6 +734,159 @@ def kapuvik_kernels(pk, sz):
     return rows
 
 
+# ---- Fovenex beside Kapuvik at equal size (`--workload fovenex`) ----------------------------------------
+# The same widths and head counts as above, four layers: latent attention (heads of 128 + 64 rotated channels, values of
+# 128, a latent row of 512 + 64, queries through a latent of 768, a window of 1,024), two layers of differential attention
+# (every head two maps of 64 channels over values of 128, grouped key/value heads, stretched rotation), and a latent layer
+# that reads the first one's rows.  Four copies of the stream; the dense feed-forward has the size that a Dobepel token runs
+# through.  Kapuvik is the closest existing model: latent attention through the same kernels, softmax attention through the
+# same tensor-core kernels, a dense feed-forward, one elementwise kernel a sublayer.
+FOVENEX_QRANK, FOVENEX_WINDOW, FOVENEX_STREAMS = 768, 1024, 4
+
+
+def fovenex_raw(sz):
+    ff = {"kind": "dense", "ff": DOBEPEL_TOP * sz["expert_ff"] + sz["shared_ff"]}
+    H = sz["heads"]
+    lat = {"heads": H, "dim": 128, "rot_dim": KAPUVIK_ROT, "vdim": 128, "kv_rank": KAPUVIK_RANK, "q_rank": FOVENEX_QRANK,
+           "scale": 192 ** -0.5, "rot": {"base": 10000.0, "dims": KAPUVIK_ROT}, "mask": {"size": FOVENEX_WINDOW}}
+    att = {"heads": H, "kv_heads": sz["kv_heads"], "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.3,
+           "rot": {"base": 10000.0, "dims": 32, "scaling": {"factor": 2.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    layers = [{"type": "latent_attention", "mixer": lat, "mlp": ff}, {"type": "attention", "mixer": att, "mlp": ff},
+              {"type": "attention", "mixer": att, "mlp": ff}, {"type": "latent_attention", "mixer": dict(lat, kv_from=0), "mlp": ff}]
+    return {"architecture": "Fovenex", "vocab": DOBEPEL_VOCAB, "width": sz["width"], "norm": {"eps": 1e-6}, "residual_mult": 0.7,
+            "streams": FOVENEX_STREAMS, "layers": json.loads(json.dumps(layers))}
+
+
+def fovenex_workload(args, pk):
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 at 2,048 cached tokens) of Fovenex and of
+    Kapuvik at equal width and depth, through the step function, timed with CUDA events; then the design's own kernels
+    beside the like kernels of Kapuvik and Qwen3 at the 2k size, each as a fraction of its roofline."""
+    import torch
+    from velox_b200.config import FovenexConfig, KapuvikConfig
+
+    T, B, CTX = 2048, 8, 2048
+    K, W = max(1, min(args.steps, 32)), max(3, args.warmup)
+    gen = torch.Generator().manual_seed(SEED)
+    sizes = {}
+    four = lambda sz: dict(sz, layers=4)
+    model_points(FovenexConfig.from_dict(fovenex_raw(four(DOBEPEL_SIZES["1k"]))), DOBEPEL_VOCAB, T, B, CTX, K, W, gen)  # thrown away
+    for name, sz in DOBEPEL_SIZES.items():
+        sz = four(sz)
+        sizes[name] = {"fovenex": model_points(FovenexConfig.from_dict(fovenex_raw(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "kapuvik": model_points(KapuvikConfig.from_dict(kapuvik_raw(sz)), DOBEPEL_VOCAB, T, B, CTX, K, W, gen),
+                       "shape": sz}
+    return {"metric": "Fovenex beside Kapuvik at equal size: prefill of %d tokens, decode at batch %d with %d cached tokens, bf16"
+                      % (T, B, CTX), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "sizes": sizes,
+            "value": sizes["2k"]["fovenex"]["decode_tok_s"], "higher_is_better": True,
+            "kernels": fovenex_kernels(pk, four(DOBEPEL_SIZES["2k"])), "peaks": pk,
+            "data": "synthetic: random weights N(0,0.02) seed 2, uniform random token ids"}
+
+
+def fovenex_kernels(pk, sz):
+    """Microseconds and fractions of the roofline of Fovenex's kernels beside the like kernels of Kapuvik and Qwen3."""
+    import torch
+    from velox_b200.csrc import ops
+    dev, bf = "cuda:0", torch.bfloat16
+    E, H, G = sz["width"], sz["heads"], sz["kv_heads"]
+    D, Dv, DL = 64, 128, 128
+    C, R, WIN = KAPUVIK_RANK, KAPUVIK_ROT, FOVENEX_WINDOW
+    T, B, CTX, S = 2048, 8, 2048, PAGE
+    rows, row, us = kernel_rows(pk)
+    ints = lambda x: torch.tensor(x, dtype=torch.int32, device=dev)
+    pages = B * (CTX // S)
+    bt = torch.arange(pages, dtype=torch.int32, device=dev).view(B, CTX // S)
+    cu, off = ints([0, T]), ints([0])
+    pos_t = ints(list(range(T)))
+    seqs, pos = ints(list(range(B))), ints([CTX - 1] * B)
+    # -- differential attention: 2 H query heads of 64 over 2 G key heads of 64 and G value heads of 128 --
+    kp2 = torch.randn((pages, 2 * G, S, D), device=dev).to(bf)
+    vp1 = torch.randn((pages, G, S, Dv), device=dev).to(bf)
+    width = 2 * (H + G) * D + G * Dv + H
+    width += (-width) % 8
+    q = torch.randn((T, width), device=dev).to(bf)
+    qd = torch.randn((B, width), device=dev).to(bf)
+    fl = 2.0 * (T * (T + 1) // 2) * (D + Dv) * 2 * H
+    nb = B * CTX * (2 * G * D + G * Dv) * 2.0
+    row("prompt differential attention: both maps (mma.sync, P in two halves, shared values, float32 out)", us(
+        lambda: ops.biased_prefill_attention(q, width, kp2, vp1, bt, cu, off, D ** -0.5, 0, 0, 0.0, 2 * H, 2 * G, D, Dv, 1, T, T,
+                                             v_share=2, out_float32=True)), fl)
+    row("decode differential attention: both maps", us(
+        lambda: ops.biased_decode_attention(qd, width, kp2, vp1, bt, seqs, pos, D ** -0.5, 0, 0, 0.0, 2 * H, 2 * G, D, Dv, B, max_kv=CTX,
+                                            v_share=2, out_float32=True), 50), 0.0, nb)
+    # the like kernel of Kapuvik: the same kernels on H heads of 128 over G key and G value heads of 128, bounded scores
+    kp = torch.randn((pages, G, S, DL), device=dev).to(bf)
+    vp = torch.randn((pages, G, S, DL), device=dev).to(bf)
+    qk = torch.randn((T, (H + 2 * G) * DL), device=dev).to(bf)
+    qkd = torch.randn((B, (H + 2 * G) * DL), device=dev).to(bf)
+    row("Kapuvik: prompt attention, bounded scores (the same kernel)", us(lambda: ops.biased_prefill_attention(
+        qk, qk.shape[1], kp, vp, bt, cu, off, DL ** -0.5, 0, 0, 0.0, H, G, DL, DL, 1, T, T, softcap=KAPUVIK_CAP)),
+        2.0 * (T * (T + 1) // 2) * 2 * DL * H)
+    row("Kapuvik: decode attention, bounded scores (the same kernel)", us(lambda: ops.biased_decode_attention(
+        qkd, qkd.shape[1], kp, vp, bt, seqs, pos, DL ** -0.5, 0, 0, 0.0, H, G, DL, DL, B, max_kv=CTX, softcap=KAPUVIK_CAP), 50),
+        0.0, B * G * CTX * 2 * DL * 2.0)
+    maps = torch.randn((T, 2 * H * Dv), device=dev)
+    row("difference of the maps + per-head norm + gate, %d tokens" % T, us(lambda: ops.diff_combine(
+        maps, q, 2 * (H + G) * D + G * Dv, 0.4, 0.7, 1e-6, H, H // G, Dv, bf)), 0.0, T * H * Dv * (8 + 2.0))
+    og = torch.randn((T, H * Dv), device=dev)
+    gg = torch.randn((T, H * Dv), device=dev).to(bf)
+    wv = torch.ones(Dv, device=dev)
+    row("Kapuvik: per-head norm + silu gate, %d tokens" % T, us(lambda: ops.head_norm_gate(og, gg, wv, H, 1e-6, "silu")), 0.0,
+        T * H * Dv * (4 + 2 + 2.0))
+    slots = torch.randperm(pages * S, device=dev)[:T].to(torch.int32)
+    inv32 = (1e4 ** (-torch.arange(0, 32, 2, device=dev, dtype=torch.float32) / 32)).contiguous()
+    qn = torch.ones(D, device=dev)
+    row("q/k norm + stretched rotation + cache write, shared values, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
+        q, qn, qn, 1e-6, inv32, 32, pos_t, slots, kp2, vp1, 2 * H, 2 * G, D, Dv, num_v_heads=G, magnitude=1.07)), 0.0,
+        T * (2 * (H + G) * D * 2 + G * Dv) * 2 * 1.0)
+    inv128 = (1e4 ** (-torch.arange(0, DL, 2, device=dev, dtype=torch.float32) / DL)).contiguous()
+    row("Qwen3/Kapuvik: q/k rotation + cache write, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
+        qk, None, None, 1e-6, inv128, DL, pos_t, slots, kp, vp, H, G, DL, DL)), 0.0, T * (H + 2 * G) * DL * 2 * 2.0)
+    # -- latent attention under a window --
+    lp = torch.randn((pages, 1, S, C + R), device=dev).to(bf)
+    qad = torch.randn((B, H, C + R), device=dev).to(bf)
+    row("decode latent attention, window %d (folded)" % WIN, us(lambda: ops.latent_attention(
+        qad, lp, bt, seqs, pos, 192 ** -0.5, H, C, R, max_kv=CTX, window=WIN), 20), 0.0, B * WIN * (C + R) * 2.0)
+    row("Kapuvik: decode latent attention, all %d rows (the same kernel)" % CTX, us(lambda: ops.latent_attention(
+        qad, lp, bt, seqs, pos, 192 ** -0.5, H, C, R, max_kv=CTX), 20), 0.0, B * CTX * (C + R) * 2.0)
+    if ops.raised_attention_supported(bf, DL + R, DL):
+        w_raise = (torch.randn((H * (2 * DL + R), C + R), device=dev) * 0.05).to(bf)
+        qr = torch.randn((T, H * (DL + R)), device=dev).to(bf)
+        for name, win in (("prompt latent attention, window %d, raised rows (mma.sync portion kernel, keys of 192)" % WIN, WIN),
+                          ("Kapuvik: prompt latent attention, no window (the same kernel)", 0)):
+            plan = ops.RaisedPlan([T], dev, [0], win)
+            kv_rows = ops.gemm_bf16(ops.latent_gather(lp, bt, cu, off, plan), w_raise)
+            pairs = sum(min(i + 1, win) if win else i + 1 for i in range(T))
+            row(name, us(lambda: ops.raised_attention(qr, qr.shape[1], kv_rows, cu, off, plan, 192 ** -0.5, H, DL + R, DL, T)),
+                2.0 * pairs * (2 * DL + R) * H)
+        # a portion of 256 tokens on 1,792 cached rows: only the window's rows are gathered and raised
+        cu2, off2 = ints([0, 256]), ints([CTX - 256])
+        for name, win in (("gather + raise for 256 new tokens at 1,792 cached, window %d" % WIN, WIN),
+                          ("Kapuvik: gather + raise for 256 new tokens at 1,792 cached, no window", 0)):
+            plan2 = ops.RaisedPlan([CTX], dev, [CTX - 256], win)
+            row(name, us(lambda: ops.gemm_bf16(ops.latent_gather(lp, bt, cu2, off2, plan2), w_raise)),
+                2.0 * plan2.rows * (C + R) * H * (2 * DL + R))
+    og2 = torch.randn((T, H * DL), device=dev).to(bf)
+    row("gate element by element, %d tokens" % T, us(lambda: ops.sigmoid_gate(og2, gg)), 0.0, T * H * DL * 6.0)
+    # -- the stream in four copies --
+    big, n = 16384, FOVENEX_STREAMS
+    xs = torch.randn((big, n * E), device=dev)
+    y = torch.randn((big, E), device=dev).to(bf)
+    w, ls = torch.ones(E, device=dev), torch.ones(E, device=dev)
+    mix = [[1.0 if a == b else 0.05 for b in range(n)] for a in range(n)]
+    coef = [0.25] * n
+    row("stream in %d copies: update + mixing + next weighted sum + layer norm, %d rows" % (n, big),
+        us(lambda: ops.stream_update(xs, n, mix, coef, 0.7, ls, y, coef, w, 1e-6), 10), 0.0, big * E * (2 * n * 4 + 2 + 2.0))
+    x1 = torch.randn((big, E), device=dev)
+    row("one copy: update + layer scale + next layer norm, %d rows" % big,
+        us(lambda: ops.stream_update(x1, 1, None, None, 0.7, ls, y, None, w, 1e-6), 10), 0.0, big * E * (4 + 4 + 2 + 2.0))
+    row("Kapuvik: stream += one term, then the next RMS norm, %d rows" % big,
+        us(lambda: ops.sum_add_rmsnorm(x1, [(y, 1.0)], weight=w, eps=1e-6), 10), 0.0, big * E * (4 + 4 + 2 + 2.0))
+    rows_i = ints(list(range(0, big, 64)))
+    row("sum of %d copies + last layer norm of %d wanted rows" % (n, big // 64),
+        us(lambda: ops.stream_norm(xs, n, None, w, 1e-6, bf, rows=rows_i), 10), 0.0, (big // 64) * E * (n * 4 + 2.0))
+    return rows
+
+
 def main() -> int:
     global CONTEXT, PROMPT
     ap = argparse.ArgumentParser()
@@ -743,12 +896,13 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (recorded in config)")
     ap.add_argument("--batch", type=int, default=BATCH)
-    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "dobepel", "buvuzen", "kapuvik"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "stream", "dobepel", "buvuzen", "kapuvik", "fovenex"],
                     help="decode: the benchmark (steady decoding at a fixed batch). stream: continuous batching "
                          "under arrivals (64 requests, prompts of 128-4,096 tokens, 256 new tokens each, Poisson "
                          "arrivals); prints its own JSON line. dobepel: the Dobepel design beside Qwen3 at equal size "
                          "(prefill, decode, and the design's kernels against their rooflines); its own JSON line. buvuzen: the same for "
-                         "the Buvuzen design beside Dobepel and Qwen3. kapuvik: the same for the Kapuvik design beside Dobepel")
+                         "the Buvuzen design beside Dobepel and Qwen3. kapuvik: the same for the Kapuvik design beside Dobepel. "
+                         "fovenex: the same for the Fovenex design beside Kapuvik")
     ap.add_argument("--arrival-rate", type=float, default=16.0, help="stream: mean arrivals a second")
     ap.add_argument("--lazy-graphs", action="store_true",
                     help="stream: capture each decode graph when a step first needs it, inside the run")
@@ -779,9 +933,9 @@ def main() -> int:
     from velox_b200.csrc import ops
     from velox_b200.engine import StepEntry
 
-    if args.workload in ("dobepel", "buvuzen", "kapuvik"):
+    if args.workload in ("dobepel", "buvuzen", "kapuvik", "fovenex"):
         with ClockSampler() as clocks:
-            res = {"dobepel": dobepel_workload, "buvuzen": buvuzen_workload, "kapuvik": kapuvik_workload}[args.workload](args, peaks())
+            res = {"dobepel": dobepel_workload, "buvuzen": buvuzen_workload, "kapuvik": kapuvik_workload, "fovenex": fovenex_workload}[args.workload](args, peaks())
         res["clocks"] = clocks.summary()
         print(json.dumps(res))
         return 0

@@ -1138,7 +1138,8 @@ def raised_attention(q: torch.Tensor, q_row_stride: int, kv: torch.Tensor, cu_se
     return out
 
 
-STREAMS_MAX = 16   # copies of the stream that the stream kernels take
+STREAMS_MAX = 16          # copies of the stream that the stream kernels take
+STREAM_MAX_WIDTH = 51200  # ... and the widest row (it lies in a block's shared memory as float32)
 
 
 def _host_floats(values, n: int, what: str):

@@ -225,6 +225,8 @@ class HyperConnectionBlock(Block):
         self.hidden_size, self.streams, self.residual_mult = int(hidden_size), int(streams), float(residual_mult)
         if not 0 <= self.streams <= ops.STREAMS_MAX:
             raise ValueError("%sa stream in %d copies: the stream kernels take up to %d" % (prefix, self.streams, ops.STREAMS_MAX))
+        if not 0 < self.hidden_size <= ops.STREAM_MAX_WIDTH:
+            raise ValueError("%sa stream of width %d: the stream kernels take up to %d" % (prefix, self.hidden_size, ops.STREAM_MAX_WIDTH))
         for name, n in self.norms.items():
             if not hasattr(n, "weight") or not hasattr(n, "eps") or getattr(n, "streams", 1) != 1:
                 raise ValueError("HyperConnectionBlock fuses its norms into the stream's update and takes layer or RMS norms of one "
