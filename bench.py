@@ -837,7 +837,7 @@ def fovenex_kernels(pk, sz):
     qn = torch.ones(D, device=dev)
     row("q/k norm + stretched rotation + cache write, shared values, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
         q, qn, qn, 1e-6, inv32, 32, pos_t, slots, kp2, vp1, 2 * H, 2 * G, D, Dv, num_v_heads=G, magnitude=1.07)), 0.0,
-        T * (2 * (H + G) * D * 2 + G * Dv) * 2 * 1.0)
+        T * (2 * (H + G) * D + G * Dv) * 2 * 2.0)
     inv128 = (1e4 ** (-torch.arange(0, DL, 2, device=dev, dtype=torch.float32) / DL)).contiguous()
     row("Qwen3/Kapuvik: q/k rotation + cache write, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
         qk, None, None, 1e-6, inv128, DL, pos_t, slots, kp, vp, H, G, DL, DL)), 0.0, T * (H + 2 * G) * DL * 2 * 2.0)

@@ -126,14 +126,17 @@ def two_maps(q, k, v, scale, window=0):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,Dv,rot,scaling", [(4, 2, 10, 12, 6, (4.0, 16, 4.0, 1.0)), (2, 1, 64, 64, 32, (2.0, 64, 16.0, 1.0)),
-                                                  (3, 3, 16, 20, 16, None), (2, 2, 128, 64, 0, None)])
-def test_norm_stretched_rotation_and_the_write_of_shared_values(dtype, H, G, D, Dv, rot, scaling):
+                                                  (3, 3, 16, 20, 16, None), (2, 2, 128, 64, 0, None), (5, 1, 72, 33, 26, (3.0, 32, 8.0, 2.0)),
+                                                  (1, 1, 200, 64, 200, None)])
+@pytest.mark.parametrize("T", [45, 130])
+def test_norm_stretched_rotation_and_the_write_of_shared_values(dtype, H, G, D, Dv, rot, scaling, T):
     """Both maps' queries and keys normed with one weight each and turned with halves paired by stretched frequencies and
-    their multiplier; the keys of 2 G heads and the values of G heads written into pools of those sizes."""
+    their multiplier; the keys of 2 G heads and the values of G heads written into pools of those sizes.  Few tokens take the
+    kernel with a warp per head, many the kernels with a block per token (heads in registers for bfloat16)."""
     from velox_b200.csrc import ops
     from velox_b200.parts.position import RotaryPosition
     rng = np.random.default_rng(D)
-    T, S = 45, 16
+    S = 16
     q, k, v = bf(rng.normal(size=(T, 2 * H, D))), bf(rng.normal(size=(T, 2 * G, D))), bf(rng.normal(size=(T, G, Dv)))
     qw, kw = bf(1.0 + 0.2 * rng.normal(size=D)), bf(1.0 + 0.2 * rng.normal(size=D))
     pos = np.arange(T) + 100
@@ -150,9 +153,9 @@ def test_norm_stretched_rotation_and_the_write_of_shared_values(dtype, H, G, D, 
         assert np.abs(inv_freq.cpu().numpy() - f).max() <= 1e-7 and abs(mag - magnitude) < 1e-12
     pad = (-(2 * (H + G) * D + G * Dv + 5)) % 8
     x = dev(np.concatenate([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1), np.full((T, 5 + pad), 7.0)], 1), dtype)
-    table = np.random.default_rng(3).permutation(9)[:3]
-    k_pool = torch.full((9, 2 * G, S, D), float("nan"), dtype=dtype, device=DEV)
-    v_pool = torch.full((9, G, S, Dv), float("nan"), dtype=dtype, device=DEV)
+    table = np.random.default_rng(3).permutation(12)[:-(-T // S)]
+    k_pool = torch.full((12, 2 * G, S, D), float("nan"), dtype=dtype, device=DEV)
+    v_pool = torch.full((12, G, S, Dv), float("nan"), dtype=dtype, device=DEV)
     slots = [int(table[j // S]) * S + j % S for j in range(T)]
     ops.qk_norm_rope_kv(x, dev(qw), dev(kw), 1e-5, inv_freq, rot, ints(pos), ints(slots), k_pool, v_pool, 2 * H, 2 * G, D, Dv,
                         num_v_heads=G, magnitude=magnitude)

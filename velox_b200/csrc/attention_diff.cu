@@ -72,6 +72,28 @@ __global__ void sigmoid_gate_kernel(const T* __restrict__ o, int ldo, const T* _
     }
 }
 
+// bfloat16 rows whose pointers and strides lie on 16-byte borders: eight elements a thread.
+__global__ void sigmoid_gate8_kernel(const bf16* __restrict__ o, int ldo, const bf16* __restrict__ g, int ldg, bf16* __restrict__ out,
+                                     int ldout, long long total8, int cols8) {
+    pdl_wait();
+    pdl_trigger();
+    for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total8; idx += (long long)gridDim.x * blockDim.x) {
+        const long long r = idx / cols8;
+        const int c = (int)(idx - r * cols8) * 8;
+        const uint4 a = *reinterpret_cast<const uint4*>(o + r * ldo + c), b = *reinterpret_cast<const uint4*>(g + r * ldg + c);
+        const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&a);
+        const __nv_bfloat162* b2 = reinterpret_cast<const __nv_bfloat162*>(&b);
+        uint4 res;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 x = __bfloat1622float2(a2[e]), z = __bfloat1622float2(b2[e]);
+            r2[e] = __floats2bfloat162_rn(x.x / (1.f + expf(-z.x)), x.y / (1.f + expf(-z.y)));
+        }
+        *reinterpret_cast<uint4*>(out + r * ldout + c) = res;
+    }
+}
+
 extern "C" int vx_sigmoid_gate(const void* o, int ldo, const void* g, int ldg, void* out, int ldout, int rows, int cols,
                                int dtype, cudaStream_t stream) {
     if (rows <= 0 || cols <= 0) return VX_OK;
@@ -81,7 +103,12 @@ extern "C" int vx_sigmoid_gate(const void* o, int ldo, const void* g, int ldg, v
     if (dtype == VX_F32)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (sigmoid_gate_kernel<float>), blocks, 256, 0, stream, (const float*)o, ldo, (const float*)g, ldg,
                     (float*)out, ldout, total, cols);
-    else if (dtype == VX_BF16)
+    else if (dtype == VX_BF16 && !((cols | ldo | ldg | ldout) & 7) && !(((uintptr_t)o | (uintptr_t)g | (uintptr_t)out) & 15)) {
+        const long long total8 = total / 8;
+        const unsigned blocks8 = (unsigned)((total8 + 255) / 256 > 148LL * 16 ? 148LL * 16 : (total8 + 255) / 256);
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, sigmoid_gate8_kernel, blocks8, 256, 0, stream, (const bf16*)o, ldo, (const bf16*)g, ldg,
+                    (bf16*)out, ldout, total8, cols / 8);
+    } else if (dtype == VX_BF16)
         VX_LAUNCH_K(VX_K_ELEMENTWISE, (sigmoid_gate_kernel<bf16>), blocks, 256, 0, stream, (const bf16*)o, ldo, (const bf16*)g, ldg,
                     (bf16*)out, ldout, total, cols);
     else

@@ -19,6 +19,25 @@
 
 #define HS_MAX_STREAMS 16
 #define HS_THREADS 256
+#define HS_MAX_THREADS 1024
+
+// VEC consecutive channels of a row at a time: float4 of the stream, 8 or 16 bytes of T.
+template <int VEC> __device__ __forceinline__ void hs_load(const float* p, float (&v)[VEC]) {
+    if constexpr (VEC == 4) { const float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    else v[0] = p[0];
+}
+template <int VEC> __device__ __forceinline__ void hs_load(const bf16* p, float (&v)[VEC]) {
+    if constexpr (VEC == 4) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+    } else v[0] = __bfloat162float(p[0]);
+}
+template <int VEC> __device__ __forceinline__ void hs_store(float* p, const float (&v)[VEC]) {
+    if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+    else p[0] = v[0];
+}
 
 struct HsCoef {
     float in[HS_MAX_STREAMS];
@@ -41,7 +60,7 @@ __device__ __forceinline__ void hs_norm_row(const float* u_s, const float* __res
 }
 
 template <typename T>
-__global__ void __launch_bounds__(HS_THREADS)
+__global__ void __launch_bounds__(HS_MAX_THREADS)
 stream_norm_kernel(const float* __restrict__ x, int n, HsCoef c, const float* __restrict__ single, float* __restrict__ copies,
                    const float* __restrict__ w, float eps, const int* __restrict__ rows, T* __restrict__ out, int E, int rms) {
     extern __shared__ float hs_u[];
@@ -77,41 +96,58 @@ struct HsMix {
     float in_next[HS_MAX_STREAMS];
 };
 
-template <typename T, int N>
-__global__ void __launch_bounds__(HS_THREADS)
+template <typename T, int N, int VEC>
+__global__ void __launch_bounds__(HS_MAX_THREADS)
 stream_update_kernel(float* __restrict__ x, int n_dyn, const __grid_constant__ HsMix m, const float* __restrict__ ls,
                      const T* __restrict__ y, int ldy, const float* __restrict__ w_next, float eps, T* __restrict__ h_out,
                      int E, int rms) {
-    extern __shared__ float hs_u[];
+    extern __shared__ __align__(16) float hs_u[];
     __shared__ float scratch[32];
+    constexpr int NMAX = N > 0 ? N : HS_MAX_STREAMS;
     const int n = N > 0 ? N : n_dyn;
     const int t = blockIdx.x;
     float* xr = x + (size_t)t * n * E;
     pdl_wait();
     pdl_trigger();
     const T* yr = y + (size_t)t * ldy;
-    for (int i = threadIdx.x; i < E; i += blockDim.x) {
-        float old[N > 0 ? N : HS_MAX_STREAMS];
+    for (int i = threadIdx.x * VEC; i < E; i += blockDim.x * VEC) {
+        float old[NMAX][VEC], b[VEC], scale[VEC], u[VEC];
 #pragma unroll
-        for (int s = 0; s < (N > 0 ? N : HS_MAX_STREAMS); ++s)
-            if (s < n) old[s] = xr[(size_t)s * E + i];
-        const float b = (ls ? ls[i] : 1.f) * to_f32(yr[i]);
-        float u = 0.f;
+        for (int s = 0; s < NMAX; ++s)
+            if (s < n) hs_load<VEC>(xr + (size_t)s * E + i, old[s]);
+        hs_load<VEC>(yr + i, b);
+        if (ls) {
+            hs_load<VEC>(ls + i, scale);
 #pragma unroll
-        for (int to = 0; to < (N > 0 ? N : HS_MAX_STREAMS); ++to) {
-            if (to >= n) break;
-            float v = m.out[to] * b;
-#pragma unroll
-            for (int s = 0; s < (N > 0 ? N : HS_MAX_STREAMS); ++s)
-                if (s < n) v = fmaf(m.mix[s * n + to], old[s], v);
-            xr[(size_t)to * E + i] = v;
-            u = fmaf(m.in_next[to], v, u);
+            for (int e = 0; e < VEC; ++e) b[e] *= scale[e];
         }
-        if (w_next) hs_u[i] = u;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) u[e] = 0.f;
+#pragma unroll
+        for (int to = 0; to < NMAX; ++to) {
+            if (to >= n) break;
+            float v[VEC];
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) {
+                v[e] = m.out[to] * b[e];
+#pragma unroll
+                for (int s = 0; s < NMAX; ++s)
+                    if (s < n) v[e] = fmaf(m.mix[s * n + to], old[s][e], v[e]);
+                u[e] = fmaf(m.in_next[to], v[e], u[e]);
+            }
+            hs_store<VEC>(xr + (size_t)to * E + i, v);
+        }
+        if (w_next) hs_store<VEC>(hs_u + i, u);
     }
     if (!w_next) return;
     __syncthreads();
     hs_norm_row<T>(hs_u, w_next, eps, h_out + (size_t)t * E, E, rms, scratch);
+}
+
+// Threads of a block for rows of E channels taken VEC at a time: one pass over the row where 1,024 threads reach.
+static int hs_threads(int E, int vec) {
+    const int want = ((E + vec - 1) / vec + 31) / 32 * 32;
+    return want < 64 ? 64 : (want > HS_MAX_THREADS ? HS_MAX_THREADS : want);
 }
 
 static int hs_fill(float* dst, const float* src, int n) {
@@ -134,11 +170,11 @@ extern "C" int vx_stream_norm(const float* x, int n, const float* in_coef, const
     static bool configured[2][VX_MAX_DEVICES];
     if (dtype == VX_F32) {
         if (int rc = vx_configure_smem(stream_norm_kernel<float>, 200 * 1024, configured[0])) return rc;
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (stream_norm_kernel<float>), count, HS_THREADS, smem, stream, x, n, c, single, copies, w, eps,
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (stream_norm_kernel<float>), count, hs_threads(E, 1), smem, stream, x, n, c, single, copies, w, eps,
                     rows, (float*)out, E, rms);
     } else if (dtype == VX_BF16) {
         if (int rc = vx_configure_smem(stream_norm_kernel<bf16>, 200 * 1024, configured[1])) return rc;
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (stream_norm_kernel<bf16>), count, HS_THREADS, smem, stream, x, n, c, single, copies, w, eps,
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (stream_norm_kernel<bf16>), count, hs_threads(E, 1), smem, stream, x, n, c, single, copies, w, eps,
                     rows, (bf16*)out, E, rms);
     } else {
         return VX_ERR_DTYPE;
@@ -166,22 +202,25 @@ extern "C" int vx_stream_update(float* x, int n, const float* mix, const float* 
     }
     const size_t smem = w_next ? (size_t)E * sizeof(float) : 0;
     static bool configured[8][VX_MAX_DEVICES];
-#define HS_GO(T, N, SLOT)                                                                                                  \
+#define HS_GO(T, N, VEC, SLOT)                                                                                             \
     do {                                                                                                                   \
-        if (int rc = vx_configure_smem(stream_update_kernel<T, N>, 200 * 1024, configured[SLOT])) return rc;               \
-        VX_LAUNCH_K(VX_K_ELEMENTWISE, (stream_update_kernel<T, N>), tokens, HS_THREADS, smem, stream, x, n, m, ls, (const T*)y, \
-                    ldy, w_next, eps, (T*)h_out, E, rms);                                                                   \
+        if (int rc = vx_configure_smem(stream_update_kernel<T, N, VEC>, 200 * 1024, configured[SLOT])) return rc;          \
+        VX_LAUNCH_K(VX_K_ELEMENTWISE, (stream_update_kernel<T, N, VEC>), tokens, hs_threads(E, VEC), smem, stream, x, n, m, ls, \
+                    (const T*)y, ldy, w_next, eps, (T*)h_out, E, rms);                                                      \
     } while (0)
+    // four channels a thread where every row starts on a 16-byte border (the general instantiation keeps one: its copies
+    // would not fit the registers of 1,024 threads)
+    const bool vec = !(E & 3) && !(ldy & 3) && !(((uintptr_t)x | (uintptr_t)ls | (uintptr_t)y) & 15);
     if (dtype == VX_F32) {
-        if (n == 1) HS_GO(float, 1, 0);
-        else if (n == 2) HS_GO(float, 2, 1);
-        else if (n == 4) HS_GO(float, 4, 2);
-        else HS_GO(float, 0, 3);
+        if (n == 1 && vec) HS_GO(float, 1, 4, 0);
+        else if (n == 2 && vec) HS_GO(float, 2, 4, 1);
+        else if (n == 4 && vec) HS_GO(float, 4, 4, 2);
+        else HS_GO(float, 0, 1, 3);
     } else if (dtype == VX_BF16) {
-        if (n == 1) HS_GO(bf16, 1, 4);
-        else if (n == 2) HS_GO(bf16, 2, 5);
-        else if (n == 4) HS_GO(bf16, 4, 6);
-        else HS_GO(bf16, 0, 7);
+        if (n == 1 && vec) HS_GO(bf16, 1, 4, 4);
+        else if (n == 2 && vec) HS_GO(bf16, 2, 4, 5);
+        else if (n == 4 && vec) HS_GO(bf16, 4, 4, 6);
+        else HS_GO(bf16, 0, 1, 7);
     } else {
         return VX_ERR_DTYPE;
     }

@@ -120,6 +120,7 @@ def _declare(lib) -> None:
         "vx_diff_combine": [P, I, P, I, I, P, F, F, F, I, I, I, I, I, P],
         "vx_sigmoid_gate": [P, I, P, I, P, I, I, I, I, P],
         "vx_rmsnorm_rows": [P, I, P, P, I, I, F, I, P],
+        "vx_gemm_few_rows_batched": [P, P, P, I, I, I, I, I, I, I, c_longlong, c_longlong, c_longlong, I, P],
         "vx_biased_attention_shared": [P, I, P, P, P, I, P, P, P, P, P, I, F, F, I, I, I, I, I, I, I, I, I, P, I, P, I, F, I, I, P],
         "vx_biased_attention_rows_window": [P, I, P, c_longlong, c_longlong, P, c_longlong, c_longlong, P, I, P, P, P, P, I, F, I, I,
                                             I, I, I, I, I, F, I, P],
@@ -902,15 +903,24 @@ def gemm_nt_simt(a: torch.Tensor, w: torch.Tensor, bias=None, out_dtype: Optiona
     return out
 
 
+GEMM_HEADS_FEW_ROWS = 8   # rows up to which the products per head take the kernel that gives every output column a warp
+
+
 def gemm_heads(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """One product per head: out[:, h, :] = a[:, h, :] w[h]^T with a [M, H, K], w [H, N, K] (contiguous), out [M, H, N];
-    `a` and `out` may be views into wider rows (their last dimension contiguous).  float32 multiply-adds."""
+    `a` and `out` may be views into wider rows (their last dimension contiguous).  float32 multiply-adds (in float32, every
+    sum over k in ascending order whatever the number of rows; bfloat16 steps of up to 8 rows take a kernel of their own)."""
     _dev(a, w, out)
     _need(a.dim() == 3 and w.dim() == 3 and out.dim() == 3 and w.is_contiguous() and a.shape[1] == w.shape[0]
           and a.shape[2] == w.shape[2] and out.shape == (a.shape[0], w.shape[0], w.shape[1]), "gemm_heads: a [M,H,K], w [H,N,K], out [M,H,N]")
     _need(a.stride(2) == 1 and out.stride(2) == 1 and a.dtype == w.dtype, "gemm_heads: rows contiguous, one element type")
     m, h, k = a.shape
     n = w.shape[1]
+    if a.dtype == torch.bfloat16 and m <= GEMM_HEADS_FEW_ROWS and k % 8 == 0 and k <= 4096 and w.data_ptr() % 16 == 0:
+        # a decode step's few rows: a warp per output column, W read once by batch * n / 8 blocks
+        _check(library().vx_gemm_few_rows_batched(_ptr(a), _ptr(w), _ptr(out), m, n, k, a.stride(0), k, out.stride(0), h, a.stride(1),
+                                                  n * k, out.stride(1), dtype_code(out.dtype), _stream()), "gemm_few_rows_heads")
+        return out
     _check(library().vx_gemm_nt_simt_batched(_ptr(a), _ptr(w), None, _ptr(out), m, n, k, a.stride(0), k, out.stride(0), h,
                                              a.stride(1), n * k, out.stride(1), dtype_code(a.dtype), dtype_code(out.dtype),
                                              _stream()), "gemm_nt_simt_heads")

@@ -89,6 +89,175 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ qkv, int row_stride,
     }
 }
 
+// The same for many tokens (a prompt portion) at any head size: one block per token works through all heads of its row,
+// eight warps taking the heads in turn, with the token's cosines and sines (times `magnitude`) computed once into shared
+// memory instead of once per head.  The arithmetic of a head is the kernel's above.
+#define ROPE_ROW_WARPS 8
+#define ROPE_ROW_MIN_TOKENS 64   // tokens from which this variant is used
+template <typename T>
+__global__ void __launch_bounds__(ROPE_ROW_WARPS * 32)
+qk_norm_rope_kv_row_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ q_weight,
+                           const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq, int rot_dim,
+                           const int* __restrict__ positions, const int* __restrict__ slot_mapping, T* __restrict__ k_pool,
+                           T* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv, int interleaved, int Hv, float magnitude) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float smem[];
+    const int half = (inv_freq && rot_dim > 0) ? rot_dim >> 1 : 0;
+    float* cs_s = smem;                 // [half] cosines, then [half] sines
+    float* bufs = smem + 2 * half;      // [warps][D]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        cs_s[i] = cs * magnitude;
+        cs_s[half + i] = sn * magnitude;
+    }
+    __syncthreads();
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    float* buf = bufs + warp * D;
+    for (int head = warp; head < H + Hk + Hv; head += ROPE_ROW_WARPS) {
+        if (head >= H + Hk) {  // value head: copy into the cache
+            if (slot < 0) continue;
+            const int hk = head - H - Hk;
+            const T* vsrc = qkv + (size_t)t * row_stride + (size_t)(H + Hk) * D + (size_t)hk * Dv;
+            T* dst = v_pool + (((size_t)(slot / S) * Hv + hk) * S + (slot % S)) * Dv;
+            for (int d = lane; d < Dv; d += 32) dst[d] = vsrc[d];
+            continue;
+        }
+        const bool is_q = head < H;
+        if (!is_q && slot_mapping && slot < 0) continue;
+        const float* w = is_q ? q_weight : k_weight;
+        T* src = qkv + (size_t)t * row_stride + (size_t)head * D;
+        float ss = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const float x = to_f32(src[d]);
+            buf[d] = x;
+            ss += x * x;
+        }
+        if (w) {
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / (float)D + eps);
+            for (int d = lane; d < D; d += 32) buf[d] = buf[d] * rstd * w[d];
+        }
+        __syncwarp();
+        for (int i = lane; i < half; i += 32) {
+            const float cs = cs_s[i], sn = cs_s[half + i];
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + half;
+            const float a = buf[ia], b = buf[ib];
+            buf[ia] = a * cs - b * sn;
+            buf[ib] = a * sn + b * cs;
+        }
+        __syncwarp();
+        T* dst = src;
+        if (!is_q && slot_mapping) dst = k_pool + (((size_t)(slot / S) * Hk + (head - H)) * S + (slot % S)) * D;
+        for (int d = lane; d < D; d += 32) dst[d] = from_f32<T>(buf[d]);
+        __syncwarp();
+    }
+}
+
+// The same again for bfloat16 heads of an even size up to 64 PAIRS elements: the head stays in registers, a lane holding the
+// element pairs (2 l, 2 l + 1) + 64 j; only the normed channels that are turned pass through shared memory, once, so that a
+// lane can read its channels' partners (i +- rot/2, or its own pair when neighbours are paired).
+template <int PAIRS>
+__global__ void __launch_bounds__(ROPE_ROW_WARPS * 32)
+qk_norm_rope_kv_row_pairs_kernel(bf16* __restrict__ qkv, int row_stride, const float* __restrict__ q_weight,
+                                 const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq, int rot_dim,
+                                 const int* __restrict__ positions, const int* __restrict__ slot_mapping, bf16* __restrict__ k_pool,
+                                 bf16* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv, int interleaved, int Hv, float magnitude) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float smem[];
+    const int half = (inv_freq && rot_dim > 0) ? rot_dim >> 1 : 0;
+    const int rot = 2 * half;
+    float* cs_s = smem;                 // [half] cosines, then [half] sines
+    float* bufs = smem + 2 * half;      // [warps][rot]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        cs_s[i] = cs * magnitude;
+        cs_s[half + i] = sn * magnitude;
+    }
+    __syncthreads();
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    float* buf = bufs + warp * rot;
+    for (int head = warp; head < H + Hk + Hv; head += ROPE_ROW_WARPS) {
+        if (head >= H + Hk) {  // value head: copy into the cache
+            if (slot < 0) continue;
+            const int hk = head - H - Hk;
+            const bf16* vsrc = qkv + (size_t)t * row_stride + (size_t)(H + Hk) * D + (size_t)hk * Dv;
+            bf16* dst = v_pool + (((size_t)(slot / S) * Hv + hk) * S + (slot % S)) * Dv;
+            if (!(Dv & 1) && !((((uintptr_t)vsrc) | ((uintptr_t)dst)) & 3)) {
+                for (int d = 2 * lane; d < Dv; d += 64)
+                    *reinterpret_cast<unsigned*>(dst + d) = *reinterpret_cast<const unsigned*>(vsrc + d);
+            } else {
+                for (int d = lane; d < Dv; d += 32) dst[d] = vsrc[d];
+            }
+            continue;
+        }
+        const bool is_q = head < H;
+        if (!is_q && slot_mapping && slot < 0) continue;
+        const float* w = is_q ? q_weight : k_weight;
+        bf16* src = qkv + (size_t)t * row_stride + (size_t)head * D;
+        float2 x[PAIRS];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) {
+            const int d = 2 * lane + 64 * j;
+            x[j] = d < D ? __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(src + d)) : make_float2(0.f, 0.f);
+            ss += x[j].x * x[j].x + x[j].y * x[j].y;
+        }
+        if (w) {
+            ss = warp_sum(ss);
+            const float rstd = rsqrtf(ss / (float)D + eps);
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const int d = 2 * lane + 64 * j;
+                if (d < D) { x[j].x = x[j].x * rstd * w[d]; x[j].y = x[j].y * rstd * w[d + 1]; }
+            }
+        }
+        if (half) {
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const int d = 2 * lane + 64 * j;
+                if (d < rot) *reinterpret_cast<float2*>(buf + d) = x[j];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int j = 0; j < PAIRS; ++j) {
+                const int d = 2 * lane + 64 * j;
+                if (d >= rot) continue;
+                if (interleaved) {   // the pair (d, d + 1) is pair d / 2 of the rotation
+                    const float cs = cs_s[d >> 1], sn = cs_s[half + (d >> 1)];
+                    const float a = x[j].x, b = x[j].y;
+                    x[j] = make_float2(a * cs - b * sn, a * sn + b * cs);
+                } else if (d < half) {   // (half is even or odd: the two channels are looked at one by one)
+                    const float a0 = x[j].x, b0 = buf[d + half];
+                    x[j].x = a0 * cs_s[d] - b0 * cs_s[half + d];
+                    if (d + 1 < half) x[j].y = x[j].y * cs_s[d + 1] - buf[d + 1 + half] * cs_s[half + d + 1];
+                    else x[j].y = buf[d + 1 - half] * cs_s[half + d + 1 - half] + x[j].y * cs_s[d + 1 - half];
+                } else {
+                    x[j].x = buf[d - half] * cs_s[half + d - half] + x[j].x * cs_s[d - half];
+                    x[j].y = buf[d + 1 - half] * cs_s[half + d + 1 - half] + x[j].y * cs_s[d + 1 - half];
+                }
+            }
+            __syncwarp();   // (the warp's next head writes the same buffer)
+        }
+        bf16* dst = src;
+        if (!is_q && slot_mapping) dst = k_pool + (((size_t)(slot / S) * Hk + (head - H)) * S + (slot % S)) * D;
+#pragma unroll
+        for (int j = 0; j < PAIRS; ++j) {
+            const int d = 2 * lane + 64 * j;
+            if (d < D) *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(x[j].x, x[j].y);
+        }
+    }
+}
+
 // The arithmetic of a head of 128 written out with explicit roundings, so that the
 // two kernels below give the same bits whatever the compiler would like to fuse.
 __device__ __forceinline__ float head128_squares(float2 lo, float2 hi) {
@@ -252,6 +421,33 @@ extern "C" int vx_qk_norm_rope_kv_shared(void* qkv, int row_stride, const float*
         VX_LAUNCH_K(VX_K_ROPE, qk_norm_rope_kv_128_kernel, grid128, ROPE128_WARPS * 32, 0, stream, (bf16*)qkv,
                     row_stride, q_weight, k_weight, eps, (rot_dim == D) ? inv_freq : (const float*)nullptr, positions,
                     slot_mapping, (bf16*)k_pool, (bf16*)v_pool, H, Hk, S);
+        VX_LAUNCH_CHECK();
+        return VX_OK;
+    }
+    if (tokens >= ROPE_ROW_MIN_TOKENS && dtype == VX_BF16 && !(D & 1) && D <= 256 && !(row_stride & 1) &&
+        !((((uintptr_t)qkv) | ((uintptr_t)k_pool)) & 3)) {
+        const size_t pairs_smem = ((size_t)rot_dim + (size_t)ROPE_ROW_WARPS * rot_dim) * sizeof(float);
+#define ROPE_PAIRS_GO(P_)                                                                                                   \
+    VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_row_pairs_kernel<P_>), tokens, ROPE_ROW_WARPS * 32, pairs_smem, stream, (bf16*)qkv, \
+                row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping, (bf16*)k_pool, (bf16*)v_pool, H, \
+                Hk, D, S, Dv, interleaved, Hv, magnitude)
+        if (D <= 64) ROPE_PAIRS_GO(1);
+        else if (D <= 128) ROPE_PAIRS_GO(2);
+        else ROPE_PAIRS_GO(4);
+#undef ROPE_PAIRS_GO
+        VX_LAUNCH_CHECK();
+        return VX_OK;
+    }
+    if (tokens >= ROPE_ROW_MIN_TOKENS) {
+        const size_t row_smem = ((size_t)rot_dim + (size_t)ROPE_ROW_WARPS * D) * sizeof(float);   // (at most 18 KB)
+        if (dtype == VX_F32)
+            VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_row_kernel<float>), tokens, ROPE_ROW_WARPS * 32, row_smem, stream, (float*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
+                (float*)k_pool, (float*)v_pool, H, Hk, D, S, Dv, interleaved, Hv, magnitude);
+        else if (dtype == VX_BF16)
+            VX_LAUNCH_K(VX_K_ROPE, (qk_norm_rope_kv_row_kernel<bf16>), tokens, ROPE_ROW_WARPS * 32, row_smem, stream, (bf16*)qkv, row_stride, q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping,
+                (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S, Dv, interleaved, Hv, magnitude);
+        else
+            return VX_ERR_DTYPE;
         VX_LAUNCH_CHECK();
         return VX_OK;
     }
