@@ -841,6 +841,9 @@ def fovenex_kernels(pk, sz):
     inv128 = (1e4 ** (-torch.arange(0, DL, 2, device=dev, dtype=torch.float32) / DL)).contiguous()
     row("Qwen3/Kapuvik: q/k rotation + cache write, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
         qk, None, None, 1e-6, inv128, DL, pos_t, slots, kp, vp, H, G, DL, DL)), 0.0, T * (H + 2 * G) * DL * 2 * 2.0)
+    qn128 = torch.ones(DL, device=dev)
+    row("Qwen3: q/k norm + rotation + cache write, %d tokens" % T, us(lambda: ops.qk_norm_rope_kv(
+        qk, qn128, qn128, 1e-6, inv128, DL, pos_t, slots, kp, vp, H, G, DL, DL)), 0.0, T * (H + 2 * G) * DL * 2 * 2.0)
     # -- latent attention under a window --
     lp = torch.randn((pages, 1, S, C + R), device=dev).to(bf)
     qad = torch.randn((B, H, C + R), device=dev).to(bf)

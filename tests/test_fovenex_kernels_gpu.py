@@ -127,7 +127,8 @@ def two_maps(q, k, v, scale, window=0):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,Dv,rot,scaling", [(4, 2, 10, 12, 6, (4.0, 16, 4.0, 1.0)), (2, 1, 64, 64, 32, (2.0, 64, 16.0, 1.0)),
                                                   (3, 3, 16, 20, 16, None), (2, 2, 128, 64, 0, None), (5, 1, 72, 33, 26, (3.0, 32, 8.0, 2.0)),
-                                                  (1, 1, 200, 64, 200, None)])
+                                                  (1, 1, 200, 64, 200, None), (3, 2, 48, 128, 24, (2.0, 32, 8.0, 1.0)), (2, 2, 32, 32, 32, None),
+                                                  (5, 2, 64, 30, 0, None)])
 @pytest.mark.parametrize("T", [45, 130])
 def test_norm_stretched_rotation_and_the_write_of_shared_values(dtype, H, G, D, Dv, rot, scaling, T):
     """Both maps' queries and keys normed with one weight each and turned with halves paired by stretched frequencies and

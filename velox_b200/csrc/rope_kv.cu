@@ -258,6 +258,98 @@ qk_norm_rope_kv_row_pairs_kernel(bf16* __restrict__ qkv, int row_stride, const f
     }
 }
 
+// And for bfloat16 heads of up to 64 channels (a multiple of 4): TWO heads a warp, sixteen lanes each, a lane holding four
+// consecutive channels (one 8-byte load and store).  A head of 64 channels is one 128-byte line, and a warp that works on
+// one such head at a time spends most of its time on what a head costs whatever its size (the norm's sum over the lanes,
+// the exchange of the turned channels, the slot's address).  Value heads are copied by whole warps afterwards.
+__global__ void __launch_bounds__(ROPE_ROW_WARPS * 32)
+qk_norm_rope_kv_row_half_kernel(bf16* __restrict__ qkv, int row_stride, const float* __restrict__ q_weight,
+                                const float* __restrict__ k_weight, float eps, const float* __restrict__ inv_freq, int rot_dim,
+                                const int* __restrict__ positions, const int* __restrict__ slot_mapping, bf16* __restrict__ k_pool,
+                                bf16* __restrict__ v_pool, int H, int Hk, int D, int S, int Dv, int interleaved, int Hv, float magnitude) {
+    pdl_wait();
+    pdl_trigger();
+    extern __shared__ float smem[];
+    const int half = (inv_freq && rot_dim > 0) ? rot_dim >> 1 : 0;
+    const int rot = 2 * half;
+    float* cs_s = smem;                 // [half] cosines, then [half] sines
+    float* bufs = smem + 2 * half;      // [warps][2 heads][rot]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int l16 = lane & 15, sub = lane >> 4;
+    const int t = blockIdx.x;
+    const float pos = (float)positions[t];
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        float sn, cs;
+        sincosf(pos * inv_freq[i], &sn, &cs);
+        cs_s[i] = cs * magnitude;
+        cs_s[half + i] = sn * magnitude;
+    }
+    __syncthreads();
+    const int slot = slot_mapping ? slot_mapping[t] : -1;
+    float* buf = bufs + (warp * 2 + sub) * rot;
+    const int d = 4 * l16;
+    for (int base = warp * 2; base < H + Hk; base += 2 * ROPE_ROW_WARPS) {
+        const int head = base + sub;
+        const bool is_q = head < H;
+        const bool live = head < H + Hk && d < D && (is_q || !slot_mapping || slot >= 0);
+        const float* w = is_q ? q_weight : k_weight;
+        bf16* src = qkv + (size_t)t * row_stride + (size_t)head * D;
+        float x[4] = {0.f, 0.f, 0.f, 0.f};
+        if (live) {
+            const uint2 raw = *reinterpret_cast<const uint2*>(src + d);
+            const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+            const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+            x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y;
+        }
+        if (q_weight || k_weight) {   // (the same for both halves of the warp: all lanes take part in the exchanges)
+            float ss = x[0] * x[0] + x[1] * x[1] + x[2] * x[2] + x[3] * x[3];
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // (stays within the head's sixteen lanes)
+            const float rstd = rsqrtf(ss / (float)D + eps);
+            if (live && w) {
+                const float4 w4 = *reinterpret_cast<const float4*>(w + d);
+                x[0] = x[0] * rstd * w4.x; x[1] = x[1] * rstd * w4.y; x[2] = x[2] * rstd * w4.z; x[3] = x[3] * rstd * w4.w;
+            }
+        }
+        if (half) {
+            if (live && d < rot) *reinterpret_cast<float4*>(buf + d) = make_float4(x[0], x[1], x[2], x[3]);   // (rot is a multiple of 4)
+            __syncwarp();
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int i = d + e;
+                if (!live || i >= rot) continue;
+                if (interleaved) {
+                    const float cs = cs_s[i >> 1], sn = cs_s[half + (i >> 1)], other = buf[i ^ 1];
+                    x[e] = (i & 1) ? other * sn + x[e] * cs : x[e] * cs - other * sn;
+                } else if (i < half) {
+                    x[e] = x[e] * cs_s[i] - buf[i + half] * cs_s[half + i];
+                } else {
+                    x[e] = buf[i - half] * cs_s[half + i - half] + x[e] * cs_s[i - half];
+                }
+            }
+            __syncwarp();   // (the warp's next heads write the same buffers)
+        }
+        if (live) {
+            bf16* dst = src;
+            if (!is_q && slot_mapping) dst = k_pool + (((size_t)(slot / S) * Hk + (head - H)) * S + (slot % S)) * D;
+            uint2 out;
+            *reinterpret_cast<__nv_bfloat162*>(&out.x) = __floats2bfloat162_rn(x[0], x[1]);
+            *reinterpret_cast<__nv_bfloat162*>(&out.y) = __floats2bfloat162_rn(x[2], x[3]);
+            *reinterpret_cast<uint2*>(dst + d) = out;
+        }
+    }
+    if (slot < 0) return;
+    for (int hk = warp; hk < Hv; hk += ROPE_ROW_WARPS) {
+        const bf16* vsrc = qkv + (size_t)t * row_stride + (size_t)(H + Hk) * D + (size_t)hk * Dv;
+        bf16* dst = v_pool + (((size_t)(slot / S) * Hv + hk) * S + (slot % S)) * Dv;
+        if (!(Dv & 3) && !((((uintptr_t)vsrc) | ((uintptr_t)dst)) & 7)) {
+            for (int c = 4 * lane; c < Dv; c += 128) *reinterpret_cast<uint2*>(dst + c) = *reinterpret_cast<const uint2*>(vsrc + c);
+        } else {
+            for (int c = lane; c < Dv; c += 32) dst[c] = vsrc[c];
+        }
+    }
+}
+
 // The arithmetic of a head of 128 written out with explicit roundings, so that the
 // two kernels below give the same bits whatever the compiler would like to fuse.
 __device__ __forceinline__ float head128_squares(float2 lo, float2 hi) {
@@ -421,6 +513,16 @@ extern "C" int vx_qk_norm_rope_kv_shared(void* qkv, int row_stride, const float*
         VX_LAUNCH_K(VX_K_ROPE, qk_norm_rope_kv_128_kernel, grid128, ROPE128_WARPS * 32, 0, stream, (bf16*)qkv,
                     row_stride, q_weight, k_weight, eps, (rot_dim == D) ? inv_freq : (const float*)nullptr, positions,
                     slot_mapping, (bf16*)k_pool, (bf16*)v_pool, H, Hk, S);
+        VX_LAUNCH_CHECK();
+        return VX_OK;
+    }
+    if (tokens >= ROPE_ROW_MIN_TOKENS && dtype == VX_BF16 && !(D & 3) && D <= 64 && !(row_stride & 3) && !(rot_dim & 3) &&
+        !((((uintptr_t)qkv) | ((uintptr_t)k_pool)) & 7) && !((((uintptr_t)q_weight) | ((uintptr_t)k_weight)) & 15)) {
+        // (the buffers' rows lie on 16-byte borders: rot_dim is a multiple of 4)
+        const size_t half_smem = ((size_t)rot_dim + (size_t)ROPE_ROW_WARPS * 2 * rot_dim) * sizeof(float);
+        VX_LAUNCH_K(VX_K_ROPE, qk_norm_rope_kv_row_half_kernel, tokens, ROPE_ROW_WARPS * 32, half_smem, stream, (bf16*)qkv, row_stride,
+                    q_weight, k_weight, eps, inv_freq, rot_dim, positions, slot_mapping, (bf16*)k_pool, (bf16*)v_pool, H, Hk, D, S, Dv,
+                    interleaved, Hv, magnitude);
         VX_LAUNCH_CHECK();
         return VX_OK;
     }
