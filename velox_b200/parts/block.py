@@ -250,7 +250,8 @@ class HyperConnectionBlock(Block):
         n, E = self.copies, self.hidden_size
         norm, link = self.norms["mixer"], self.links[0]
         dtype = self.mixer.runtime.dtype
-        if residual.shape[1] == E and n > 1 or (residual.shape[1] == E and not isinstance(delta, PendingStreams)):
+        plain = residual.shape[1] == E and (n > 1 or not isinstance(delta, PendingStreams))
+        if plain:
             # the embedding's output (or a plain stream left by another kind of block): the copies start equal to it
             if isinstance(delta, PendingSum):
                 delta.add_to(residual)
